@@ -1,8 +1,8 @@
 """B200-native (sm_100a) alpha-entmax / Lazy Attention operators behind the reference's API."""
 from .ops import (adasplash, adasplash_no_block_mask, check_status, entmax_attention_forward,  # noqa: F401
-                  last_call_info, lazy_attention_triton, read_status, set_path, triton_entmax,
+                  last_call_info, lazy_attention_triton, read_status, set_flags, set_path, triton_entmax,
                   unpack_block_mask)
 
 __all__ = ["adasplash", "adasplash_no_block_mask", "triton_entmax", "lazy_attention_triton",
            "entmax_attention_forward", "unpack_block_mask", "set_path", "last_call_info",
-           "read_status", "check_status"]
+           "read_status", "check_status", "set_flags"]

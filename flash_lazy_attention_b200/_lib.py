@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libflashlazy.so")
 FLA_F32, FLA_F16, FLA_BF16 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
 PATH_NAMES = {PATH_AUTO: "auto", PATH_SIMT: "simt", PATH_TCGEN05: "tcgen05"}
+FLAG_NO_CANDIDATE_LIST, FLAG_PLAIN_FIRST_STEP = 1, 2
 
 
 class Tensor4(C.Structure):
@@ -24,7 +25,7 @@ class Tensor4(C.Structure):
 class AttnGeom(C.Structure):
     _fields_ = [("B", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("D", C.c_int32),
                 ("dtype", C.c_int32), ("causal", C.c_int32), ("varlen", C.c_void_p),
-                ("path", C.c_int32), ("status", C.c_void_p)]
+                ("path", C.c_int32), ("status", C.c_void_p), ("flags", C.c_int32)]
 
 
 _P4 = C.POINTER(Tensor4)
@@ -41,7 +42,9 @@ SIGNATURES = {
     "fla_entmax_fwd": (C.c_int, [_vp, _vp, _i64, _i64, _f32, C.c_int, C.c_int, C.c_int, _vp]),
     "fla_entmax_bwd": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _f32, C.c_int, _vp]),
     "fla_block_mask_words": (_i64, [_i32]),
-    "fla_entmax_attn_fwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, C.c_int, _vp, _vp, _vp, _vp, _vp]),
+    "fla_check_status": (C.c_int, [_vp, _vp]),
+    "fla_entmax_attn_fwd_workspace": (_sz, [_PG]),
+    "fla_entmax_attn_fwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, C.c_int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fla_entmax_attn_bwd_workspace": (_sz, [_PG]),
     "fla_entmax_attn_bwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, _vp, _vp, _vp, _vp, _P4, _P4, _P4,
                                       _vp, _sz, _vp]),
@@ -65,8 +68,7 @@ def load() -> C.CDLL:
         return _lib
     with _lock:
         if _lib is None:
-            # FLASHLAZY_LIB selects another build of the same library (the instrumented one of timeline.py)
-            path = os.environ.get("FLASHLAZY_LIB") or LIB_PATH
+            path = LIB_PATH
             if not os.path.exists(path):
                 raise RuntimeError(
                     f"{path} is missing: build it with `python -m flash_lazy_attention_b200.build` "

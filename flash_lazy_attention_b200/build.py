@@ -1,9 +1,6 @@
 """In-tree nvcc build of libflashlazy.so (sm_100a only).
 
-    python -m flash_lazy_attention_b200.build [--force] [--verbose] [--trace]
-
---trace additionally builds libflashlazy_trace.so, the same library with the tensor-core kernels
-compiled with -DFLA_TRACE (clock64 records of one CTA, read by timeline.py).
+    python -m flash_lazy_attention_b200.build [--force] [--verbose]
 
 Objects are cached under csrc/build/ keyed by source mtime; the shared library lands
 next to this file so that it travels with the source tree.
@@ -20,7 +17,6 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libflashlazy.so")
-TRACE_LIB = os.path.join(HERE, "libflashlazy_trace.so")
 SOURCES = ["fla_api.cu", "simt_attn.cu", "entmax_rows.cu", "tc_selftest.cu", "tc_attn.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
@@ -72,23 +68,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_trace() -> str:
-    """The library with the instrumented tensor-core kernels (development tool)."""
-    build()
-    obj = os.path.join(OBJ, "tc_attn_trace.o")
-    src = os.path.join(CSRC, "tc_attn.cu")
-    if not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), _newest_header()):
-        res = subprocess.run([_nvcc(), *NVCC_FLAGS, "-DFLA_TRACE", "-c", src, "-o", obj], capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"nvcc failed for the trace build:\n{res.stderr[-6000:]}")
-    objs = [obj] + [os.path.join(OBJ, s.replace(".cu", ".o")) for s in SOURCES if s != "tc_attn.cu"]
-    res = subprocess.run([_nvcc(), "-shared", "-cudart", "static", "-o", TRACE_LIB, *objs], capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"link failed:\n{res.stderr[-4000:]}")
-    return TRACE_LIB
-
-
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
-    if "--trace" in sys.argv:
-        print(build_trace())

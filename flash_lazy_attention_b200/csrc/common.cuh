@@ -47,8 +47,20 @@ struct AttnParams {
   float* dtau;
   // backward scratch
   float* delta;  // [B,H,L]
-  int debug;     // timing experiments only (FLA_DEBUG environment variable); 0 in normal use
+  // forward scratch of the tensor-core entmax kernel: per-SM candidate lists (see tc_fwd.cuh)
+  float* list_ws;
+  int list_slots;   // SM slots the workspace holds
+  int list_cap;     // entries per row thread
+  int flags;        // FLA_FLAG_* of fla_attn_geom
+  int debug;        // development builds (-DFLA_TRACE) only: timing switches; always 0 in the shipped library
 };
+
+// Timing switches exist only in development builds; the shipped kernels contain none of them.
+#ifdef FLA_TRACE
+#define FLA_DBG(p, bit) (((p).debug & (bit)) != 0)
+#else
+#define FLA_DBG(p, bit) false
+#endif
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

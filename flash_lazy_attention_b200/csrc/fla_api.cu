@@ -126,15 +126,17 @@ static void fill_common(AttnParams& p, const fla_attn_geom* g) {
   p.causal = g->causal;
   p.varlen = g->varlen;
   p.scale = 1.0f / sqrtf((float)g->D);
-  // FLA_DEBUG: switches for timing experiments on the tensor-core kernels (a sum of bits; unset in
-  // normal use).  Results are WRONG with bits 1, 2, 4, 32, 64 and unchanged in meaning with 128, 256.
+  p.flags = g->flags;
+#ifdef FLA_TRACE
+  // Development builds only: FLA_DEBUG (read once) switches single pieces of the tensor-core kernels
+  // off for timing experiments; results are wrong with most of them.  The shipped library has none.
   //   1   forward threshold passes: skip the row arithmetic        2   ... skip the score products
   //   4   forward: exactly five threshold passes
   //   32  backward: do not launch the dK/dV kernel                 64  ... the dQ kernel
-  //   128 alpha = 1.5: plain Halley first step instead of the tail-model step
-  //   256 forward: the row-max pass marks every tile for the first threshold pass
-  const char* dbg = getenv("FLA_DEBUG");
-  p.debug = dbg ? atoi(dbg) : 0;
+  //   256 forward: the row-max pass marks every tile
+  static const int dbg = [] { const char* v = getenv("FLA_DEBUG"); return v ? atoi(v) : 0; }();
+  p.debug = dbg;
+#endif
 }
 
 // Runs `mode` forward or backward on the family the geometry selects.
@@ -165,7 +167,7 @@ using namespace fla;
 
 extern "C" {
 
-int fla_version(void) { return 1000; }
+int fla_version(void) { return 1100; }
 const char* fla_last_error(void) { return g_err; }
 int fla_last_path(void) { return g_last_path; }
 
@@ -220,9 +222,52 @@ int fla_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_
   return e == cudaSuccess ? FLA_OK : cuda_fail(e, "entmax backward launch");
 }
 
+// Candidate lists of the tensor-core forward: entries per row thread and bytes per SM slot.
+static int list_cap_for(int L) {
+  // A row thread sees a quarter of the row.  Short rows: room for all of it; long rows: a sixteenth
+  // of the row (a Gaussian row keeps 7-11 % against the running maximum), at most 2048; plus the 64
+  // entries one tile may add after the last check.
+  const int quarter = (L + 3) / 4, sixteenth = L / 16;
+  int cap = quarter < 512 ? quarter : (sixteenth > 512 ? sixteenth : 512);
+  if (cap > 2048) cap = 2048;
+  return ((cap + 63) & ~63) + 64;
+}
+static size_t list_slot_bytes(int L) { return (size_t)list_cap_for(L) * 512 * sizeof(float); }
+static int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int counts[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  if (counts[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) counts[dev] = n;
+  }
+  return counts[dev];
+}
+
+size_t fla_entmax_attn_fwd_workspace(const fla_attn_geom* g) {
+  if (!g || g->B <= 0 || g->H <= 0 || g->L <= 0 || g->path == FLA_PATH_SIMT) return 0;
+  if (g->dtype != FLA_BF16 && g->dtype != FLA_F16) return 0;
+  if (g->D != 64 && g->D != 128) return 0;
+  return (size_t)sm_count() * list_slot_bytes(g->L);
+}
+
+int fla_check_status(const int32_t* status, void* stream) {
+  if (!status) return fail(FLA_ERR_INVALID, "status is NULL");
+  int32_t host[4] = {0, 0, 0, 0};
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(host, status, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the status words");
+  if (host[0] != 0)
+    return fail(FLA_ERR_DEVICE, "a bounded wait ran out in a tensor-core kernel (wait %d, block %d): results of that launch are not valid",
+                host[1], host[2]);
+  return FLA_OK;
+}
+
 int fla_entmax_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_tensor4* k, const fla_tensor4* v,
                         const fla_tensor4* o, float alpha, int niter, float* tau, float* aux_o, float* aux_s,
-                        uint32_t* block_mask, void* stream) {
+                        uint32_t* block_mask, void* workspace, size_t workspace_bytes, void* stream) {
   FLA_TRY(check_geom(g));
   if (!(alpha > 1.0f && alpha <= 2.0f)) return fail(FLA_ERR_INVALID, "alpha must be in (1, 2], got %g", alpha);
   if (niter < 0) return fail(FLA_ERR_INVALID, "niter must be >= 0");
@@ -237,6 +282,15 @@ int fla_entmax_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_
   p.alpha = alpha; p.niter = niter; p.tau = tau; p.aux_o = aux_o; p.aux_s = aux_s;
   p.block_mask = block_mask;
   p.mask_words = (int)fla_block_mask_words(g->L);
+  if (workspace && ((uintptr_t)workspace & 255) != 0) return fail(FLA_ERR_INVALID, "workspace must be 256-byte aligned");
+  if (workspace) {
+    const size_t slots = workspace_bytes / list_slot_bytes(g->L);
+    if (slots > 0) {
+      p.list_ws = (float*)workspace;
+      p.list_slots = (int)(slots > 4096 ? 4096 : slots);
+      p.list_cap = list_cap_for(g->L);
+    }
+  }
   cudaStream_t st = (cudaStream_t)stream;
   if (block_mask) {
     size_t bytes = (size_t)g->B * g->H * ((g->L + 127) / 128) * p.mask_words * sizeof(uint32_t);
@@ -300,7 +354,8 @@ static float* static_delta_ptr(int* rc) {
   if (!ptrs[dev]) {
     float* ptr = nullptr;
     e = cudaGetSymbolAddress((void**)&ptr, g_static_delta);
-    if (e != cudaSuccess || !ptr) { *rc = cuda_fail(e, "cudaGetSymbolAddress(static scratch)"); return nullptr; }
+    if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaGetSymbolAddress(static scratch)"); return nullptr; }
+    if (!ptr) { *rc = fail(FLA_ERR_CUDA, "cudaGetSymbolAddress(static scratch) returned a null address"); return nullptr; }
     ptrs[dev] = ptr;
   }
   *rc = FLA_OK;
@@ -405,7 +460,7 @@ int fla_lazy_attn_bwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_te
 
 int fla_selftest_umma(const void* a, const void* b, float* c, int variant, int32_t* status, void* stream) {
   if (!a || !b || !c || !status) return fail(FLA_ERR_INVALID, "NULL argument");
-  if (variant < 0 || variant > 2) return fail(FLA_ERR_INVALID, "variant must be 0, 1 or 2");
+  if (variant < 0 || variant > 3) return fail(FLA_ERR_INVALID, "variant must be 0, 1, 2 or 3");
   CUtensorMap ma, mb;
   const int64_t stride[4] = {128 * 128, 128 * 128, 128, 1};
   const char* err = "";

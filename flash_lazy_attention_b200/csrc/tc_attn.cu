@@ -98,11 +98,11 @@ cudaError_t launch_bwd(const BwdMaps& m, const AttnParams& p, int* status, cudaS
   if (e != cudaSuccess) return e;
   const unsigned grid = (unsigned)(((p.L + 127) / 128) * p.B * p.H);
   // dq_kernel first: its first sweep produces the row scalars delta that dkdv_kernel reads
-  // (debug bits 64 / 32 leave out one of the two launches: timing experiments only)
-  if (!(p.debug & 64)) kq<<<grid, tc::kBwdThreads, smem, st>>>(mq, mk, mv, mdo, p, status);
+  // (development builds can leave out one of the two launches for timing experiments)
+  if (!FLA_DBG(p, 64)) kq<<<grid, tc::kBwdThreads, smem, st>>>(mq, mk, mv, mdo, p, status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  if (!(p.debug & 32)) kkv<<<grid, tc::kKvThreads, smem_kv, st>>>(m.q64, mk, mv, m.do64, p, status);
+  if (!FLA_DBG(p, 32)) kkv<<<grid, tc::kKvThreads, smem_kv, st>>>(m.q64, mk, mv, m.do64, p, status);
   return cudaGetLastError();
 }
 

@@ -95,13 +95,16 @@ __device__ __forceinline__ void prob_terms(float x, float e, float tau_row, bool
 
 // dQ[128 x D] (+)= dS[128 x 128] . K[128 x D] with the 16-bit dS operand in two pieces of tensor
 // memory: keys 0-63 in columns [0, 32) of the buffer, keys 64-127 in columns [64, 96).
+// `nks`: 16-key steps to issue (fewer than 8 for the tile that reaches into a sequence's padding).
 template <int D, int FMT>
-__device__ __forceinline__ void issue_tn_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate) {
+__device__ __forceinline__ void issue_tn_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
+                                               int nks = 8) {
   constexpr uint32_t idesc = make_idesc2(128, D, FMT, FMT, 0, 1);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
-    umma_ts(d_tmem, a_tmem + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes),
-            idesc, (accumulate || ks > 0) ? 1u : 0u);
+    if (ks < nks)
+      umma_ts(d_tmem, a_tmem + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes),
+              idesc, (accumulate || ks > 0) ? 1u : 0u);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -273,7 +276,12 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           const int g = nact + t, bsel = t & 1;
           ok = ok && mbar_wait(&sh.ds_full[bsel], (t >> 1) & 1, abort_flag, status, 50);
           tc_fence_after_sync();
-          if (ok) issue_tn_split<D, FMT>(tmem_acc, tmem + 128 + 128 * bsel, k_addr(g), t > 0);
+          // keys beyond the end of the sequence: padding rows of K stay out of the reduction
+          // (S of this tile has completed: dS exists), see zero_tail_rows
+          int nks = 8;
+          const int valid = len - (int)sh.tiles[t] * 128;
+          if (ok && valid < 128) nks = zero_tail_rows(ring + k_slot(g) * Cfg::kTileBytes, valid, Cfg::kBoxes, 128);
+          if (ok) issue_tn_split<D, FMT>(tmem_acc, tmem + 128 + 128 * bsel, k_addr(g), t > 0, nks);
           umma_commit(&sh.dq_done[bsel]);
           umma_commit(&sh.k_empty[k_slot(g)]);
           DQTRACE(true, g, 12);
@@ -417,7 +425,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             float pv, w;
             bool m;
             prob_terms<MODE, KIND>(xs, e, tau_row, valid, pv, w, m);
-            const float dp = __uint_as_float(gq[x]);
+            // (a masked dP comes from padding rows of V or dO and may be anything: selected, never multiplied)
+            const float dp = (MODE == LAZY || m) ? __uint_as_float(gq[x]) : 0.f;
             if (MODE == ENTMAX) {
               if (x & 1) { acc_a1 = fmaf(w, dp, acc_a1); acc_b1 += w; } else { acc_a0 = fmaf(w, dp, acc_a0); acc_b0 += w; }
             } else {
@@ -582,7 +591,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
               bool m;
               prob_terms<MODE, KIND>(xs, e, tau_row, valid, pv, w, m);
               const float dp = __uint_as_float(gq[x + y]);
-              const float ds = MODE == ENTMAX ? w * (dp - delta) : w * ((m ? dp : 0.f) - delta);
+              // masked entries: exactly zero, whatever dP holds there (padding may be NaN)
+              const float ds = MODE == ENTMAX ? (m ? w * (dp - delta) : 0.f) : (valid ? w * ((m ? dp : 0.f) - delta) : 0.f);
               dsv[y] = ds;
               if (MODE == LAZY && want_dbias && in_window && ds != 0.f) {
                 const int dist = i - (kt * 128 + c0 + c);

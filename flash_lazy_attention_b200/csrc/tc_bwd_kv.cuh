@@ -60,15 +60,17 @@ __device__ __forceinline__ void issue_nt_n(uint32_t d_tmem, uint32_t a_addr, uin
 // tile whose rows are the reduction dimension; b_box = bytes of one 64-column box (KR * 128).
 // The 16-bit A operand comes in two pieces: reduction rows 0..KR/2-1 at a_tmem, the rest 32 columns
 // further on (each of the two threads of a key row writes its half inside the columns it read).
+// `nks`: 16-row steps to issue (fewer for the sub-tile that reaches into a sequence's padding).
 template <int D, int FMT, int KR>
 __device__ __forceinline__ void issue_tn_k(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t b_box,
-                                           bool accumulate) {
+                                           bool accumulate, int nks = KR / 16) {
   constexpr uint32_t idesc = make_idesc(128, D, FMT, 0, 1);
   constexpr int kSteps = KR / 16;
 #pragma unroll
   for (int ks = 0; ks < kSteps; ++ks)
-    umma_ts(d_tmem, a_tmem + (ks < kSteps / 2 ? ks * 8 : 32 + (ks - kSteps / 2) * 8), desc_mnmajor(b_addr + ks * 2048, b_box),
-            idesc, (accumulate || ks > 0) ? 1u : 0u);
+    if (ks < nks)
+      umma_ts(d_tmem, a_tmem + (ks < kSteps / 2 ? ks * 8 : 32 + (ks - kSteps / 2) * 8), desc_mnmajor(b_addr + ks * 2048, b_box),
+              idesc, (accumulate || ks > 0) ? 1u : 0u);
 }
 
 template <int MODE, int D, int FMT, int KIND>
@@ -200,10 +202,19 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__
           bool ok = mbar_wait(&sh.p_full[g], (n >> 1) & 1, abort_flag, status, 64);
           DQTRACE(true, n, 5);
           tc_fence_after_sync();
-          if (ok) issue_tn_k<D, FMT, 64>(tmem_dv, tmem + g * 64, do_addr, kSubBox, n > 0);          // dV += P^T . dO
+          // query rows beyond the end of the sequence: padding rows of Q and dO stay out of the
+          // reductions (the score products of this sub-tile have completed), see zero_tail_rows
+          int nks = 4;
+          const int valid = len - (int)sh.subs[n] * 64;
+          if (ok && valid < 64) {
+            uint8_t* stage = ring + s * 2 * kSubBytes;
+            zero_tail_rows(stage, valid, Cfg::kBoxes, 64);
+            nks = zero_tail_rows(stage + kSubBytes, valid, Cfg::kBoxes, 64);
+          }
+          if (ok) issue_tn_k<D, FMT, 64>(tmem_dv, tmem + g * 64, do_addr, kSubBox, n > 0, nks);          // dV += P^T . dO
           ok = ok && mbar_wait(&sh.ds_full[g], (n >> 1) & 1, abort_flag, status, 65);
           tc_fence_after_sync();
-          if (ok) issue_tn_k<D, FMT, 64>(tmem_dk, tmem + 128 + g * 64, q_addr, kSubBox, n > 0);     // dK += dS^T . Q
+          if (ok) issue_tn_k<D, FMT, 64>(tmem_dk, tmem + 128 + g * 64, q_addr, kSubBox, n > 0, nks);     // dK += dS^T . Q
           umma_commit(&sh.kd_done[g]);
           umma_commit(&sh.ring_empty[s]);
           DQTRACE(true, n, 6);
@@ -321,7 +332,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__
                 prob_terms<MODE, KIND>(xs, e, s2[x + y], valid, pv, w, m);
                 const float dp = __uint_as_float(g32[x + y]);
                 pvv[y] = pv;
-                dsv[y] = MODE == ENTMAX ? w * (dp + s1[x + y]) : w * ((m ? dp : 0.f) - s1[x + y]);
+                // masked entries: exactly zero, whatever dP holds there (padding may be NaN)
+                dsv[y] = MODE == ENTMAX ? (m ? w * (dp + s1[x + y]) : 0.f) : (valid ? w * ((m ? dp : 0.f) - s1[x + y]) : 0.f);
               }
               pk[x >> 1] = pack16<FMT>(pvv[0], pvv[1]);
               dk[x >> 1] = pack16<FMT>(dsv[0], dsv[1]);

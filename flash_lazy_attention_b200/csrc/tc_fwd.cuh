@@ -69,6 +69,10 @@ struct FwdShared {
   uint32_t act[2][32], act_next[32], act_base[32];
   uint64_t pass_ack;   // the producer and both issuers have read the verdict of the last pass
   int force_all;
+  // Running score maximum of each of the four threads of a row during the row-max pass.  Read by
+  // the other three without synchronisation: a stale value is a smaller one, and any lower bound of
+  // the row maximum keeps the candidate filter below a superset filter.
+  float rmax[4][128];
 };
 
 template <int D>
@@ -97,13 +101,40 @@ __device__ __forceinline__ void issue_nt(uint32_t d_tmem, uint32_t a_addr, uint3
 // O[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory (two 16-bit values per column,
 // format AFMT), B a [128 rows x D] tile in shared memory (format FMT) whose rows are the
 // reduction dimension (MN-major).
+// `nks` (1..8): number of 16-row steps of the reduction dimension to issue; fewer than 8 for the one
+// tile that reaches beyond the end of a sequence (see zero_tail_rows).
 template <int D, int AFMT, int FMT>
-__device__ __forceinline__ void issue_tn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate) {
+__device__ __forceinline__ void issue_tn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
+                                         int nks = 8) {
   constexpr uint32_t idesc = make_idesc2(128, D, AFMT, FMT, 0, 1);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
-    umma_ts(d_tmem, a_tmem + ks * 8, desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
-            (accumulate || ks > 0) ? 1u : 0u);
+    if (ks < nks)
+      umma_ts(d_tmem, a_tmem + ks * 8, desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
+              (accumulate || ks > 0) ? 1u : 0u);
+}
+
+// Rows of q, k, v, dO at or beyond a sequence's length are padding and may hold anything, NaN
+// included (the reference masks every load, lazy_attention_triton.py:41,56,171,215-232).  A score
+// computed from a padding row is replaced by the row threads before it is used, but a tile that is
+// the reduction operand of a second product (V in P.V, K in dS.K, Q and dO in dS^T.Q and P^T.dO)
+// would multiply its padding by the zeros standing in the other operand, and 0 * NaN is NaN.  So
+// for the one tile of a sequence that straddles its end, the issuing thread leaves the reduction
+// steps that lie wholly in the padding away (`nks` above) and clears the padding rows of the last,
+// partial step in shared memory before it issues.  Row r of a tile occupies bytes [128 r, 128 r + 128)
+// of every 64-column box, whatever the swizzle.  `rows_per_box`: 128, or 64 for the sub-tiles of the
+// dK/dV kernel.  Returns the number of 16-row steps to issue.
+__device__ __forceinline__ int zero_tail_rows(uint8_t* tile, int valid_rows, int boxes, int rows_per_box) {
+  const int nks = (valid_rows + 15) >> 4;
+  const int r1 = min(nks * 16, rows_per_box);
+  if (valid_rows < r1) {
+    for (int box = 0; box < boxes; ++box) {
+      uint4* row = (uint4*)(tile + (size_t)box * rows_per_box * 128 + (size_t)valid_rows * 128);
+      for (int x = 0; x < (r1 - valid_rows) * 8; ++x) row[x] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();   // generic-proxy stores before the tensor core's reads
+  }
+  return nks;
 }
 
 __device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
@@ -119,6 +150,10 @@ __device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
 constexpr float kTauTolHalley = 1e-2f;
 constexpr float kTauTolNewton = 1e-3f;
 constexpr float kTauTol = 1e-4f;   // after a bisected step
+// The same limits for the iteration on candidate lists, where one more iteration is cheap.
+constexpr float kListTolHalley = 1e-3f;
+constexpr float kListTolNewton = 1e-4f;
+constexpr float kListTol = 1e-5f;
 
 #ifdef FLA_TRACE
 // Development instrumentation (builds with -DFLA_TRACE only; see timeline.py of the package): CTA 0
@@ -191,6 +226,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     fence_mbar_init();
   }
   if (tid < kMaxMaskWords) sh.mask_words[tid] = 0;
+  if (tid < kFwdRowThreads) (&sh.rmax[0][0])[tid] = -INFINITY;
   if (tid < 32) {
     const int lo = tid * 32;
     sh.act[0][tid] = sh.act[1][tid] = nkt >= lo + 32 ? 0xffffffffu : (nkt > lo ? (1u << (nkt - lo)) - 1u : 0u);
@@ -301,17 +337,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for_each_tile(pass, [&](int kt) {
           if ((sn & 1u) == me) {
             const uint32_t sb = sn & 3u;   // four score buffers in flight
-            TRACE(true, pass == 1 ? 1 : 0, kt, 0, trace_clock());
+            TRACE(true, pass == 0 ? 1 : 0, kt, 0, trace_clock());
             const uint32_t st = rp.stage();
             bool ok = mbar_wait(&sh.ring_full[st], rp.phase(), abort_flag, status, 21);
-            TRACE(true, pass == 1 ? 1 : 0, kt, 1, trace_clock());
+            TRACE(true, pass == 0 ? 1 : 0, kt, 1, trace_clock());
             ok = ok && mbar_wait(&sh.s_free[sb], ((sn >> 2) & 1u) ^ 1u, abort_flag, status, 22);
-            TRACE(true, pass == 1 ? 1 : 0, kt, 2, trace_clock());
+            TRACE(true, pass == 0 ? 1 : 0, kt, 2, trace_clock());
             tc_fence_after_sync();
-            if (ok && !(p.debug & 2)) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
+            if (ok && !FLA_DBG(p, 2)) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
             umma_commit(&sh.ring_empty[st]);
             umma_commit(&sh.s_full[sb]);
-            TRACE(true, pass == 1 ? 1 : 0, kt, 3, trace_clock());
+            TRACE(true, pass == 0 ? 1 : 0, kt, 3, trace_clock());
             ++issued;
           }
           rp.advance();
@@ -333,6 +369,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       int nfin = 0;
       for (int w = 0; w * 32 < nkt; ++w) nfin += __popc(((volatile uint32_t*)sh.act[pass & 1u])[w]);
       const bool score_role = (sn & 1u) == me;
+      // the last key tile of the sequence may reach into its padding: if it is visited at all, it is
+      // visited last (ascending order)
+      const int tail_valid = len - (nkt - 1) * 128;
+      const bool tail_visited = nkt > 0 && tail_valid < 128 &&
+                                ((((volatile uint32_t*)sh.act[pass & 1u])[(nkt - 1) >> 5] >> ((nkt - 1) & 31)) & 1u) != 0u;
       for (int t = 0; t < nfin; ++t) {
         const uint32_t sb = (uint32_t)t & 1u;
         const uint32_t ofs = score_role ? fin_k_ofs(t) : fin_v_ofs(t, nfin);
@@ -353,7 +394,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           ok = ok && mbar_wait(&sh.p_full[sb], (t >> 1) & 1, abort_flag, status, 26);
           TRACE(true, 3, t, 2, trace_clock());
           tc_fence_after_sync();
-          if (ok) issue_tn<D, FMT, FMT>(tmem_o, tmem + kProbCol + sb * 64, ring_addr + st * Cfg::kTileBytes, t > 0);
+          int nks = 8;
+          if (ok && tail_visited && t == nfin - 1) nks = zero_tail_rows(ring + st * Cfg::kTileBytes, tail_valid, Cfg::kBoxes, 128);
+          if (ok) issue_tn<D, FMT, FMT>(tmem_o, tmem + kProbCol + sb * 64, ring_addr + st * Cfg::kTileBytes, t > 0, nks);
           umma_commit(&sh.ring_empty[st]);
           umma_commit(&sh.pv_done[sb]);
           TRACE(true, 3, t, 3, trace_clock());
@@ -418,10 +461,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       if (MODE == ENTMAX) {
         const float c1 = p.scale * (p.alpha - 1.f);
         const float e = 1.f / (p.alpha - 1.f);
-        // Row-max pass.  It also marks the tiles the first threshold pass has to visit: tau never
+        // Row-max pass.  It also marks the tiles a threshold pass has to visit: tau never
         // drops below max - 1, so a tile counts only if it holds a score within 1 of the row
-        // maximum; tested against the maximum this thread has seen so far (never above the final
-        // one), which marks a superset.
+        // maximum; tested against the largest score the four threads of the row have seen so far
+        // (never above the final maximum), which marks a superset.
+        //
+        // Candidate list.  Only scores within 1 (in (alpha-1)*score units) of the row maximum can
+        // ever lie above the threshold, a few percent of a long Gaussian row.  While it looks for the
+        // maximum, every row thread appends the scores of its columns that pass that test against
+        // the running maximum to a list of its own in global memory (a superset again: the running
+        // maximum only rises).  The threshold is then iterated on the lists alone: no further
+        // score products, no key tile read again, and the iteration can afford to converge fully.
+        // The lists live in a workspace slot of the SM this CTA runs on (one CTA per SM: each
+        // holds all of its tensor memory); entry x of thread t sits at slot + (x * 512 + t) floats.
+        // A thread whose list would not fit sets the overflow flag; if any does (wide supports:
+        // alpha near 1, tiny scores), or without a workspace, the CTA falls back to threshold
+        // passes over recomputed score tiles.
         float mrow = -INFINITY;
         uint32_t mark_bits = 0;
         int mark_word = 0;
@@ -430,10 +485,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (any != 0u && lane == 0) atomicOr(&sh.act_next[mark_word], any);
           mark_bits = 0;
         };
+        uint32_t smid;
+        asm("mov.u32 %0, %%smid;" : "=r"(smid));
+        bool lovf = p.list_ws == nullptr || (int)smid >= p.list_slots || p.niter <= 0 || p.list_cap < 64 ||
+                    (p.flags & FLA_FLAG_NO_CANDIDATE_LIST) != 0;
+        float* const lbase = lovf ? nullptr : p.list_ws + ((size_t)smid * (size_t)p.list_cap) * kFwdRowThreads + tid;
+        float* lw = lbase;
+        // a tile may add up to 64 entries: appending stops once fewer than that are left
+        float* const lstop = lovf ? nullptr : lbase + (size_t)(p.list_cap - 64) * kFwdRowThreads;
+        const float inv_c1 = 1.f / c1;
+        volatile float* rmx = &sh.rmax[0][0];
         for_my_tiles(0, [&](int kt, uint32_t cs) {
           const uint32_t buf = cs & 3;
           if ((kt >> 5) != mark_word) { publish_marks(); mark_word = kt >> 5; }
+          TRACE((tid & 127) == 0 && half == 0, 1, kt, 4, trace_clock());
           mbar_wait(&sh.s_full[buf], (cs >> 2) & 1, abort_flag, status, 30);
+          TRACE((tid & 127) == 0 && half == 0, 1, kt, 5, trace_clock());
           __syncwarp();
           tc_fence_after_sync();
           uint32_t r[64];
@@ -441,6 +508,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           tc_fence_before_sync();
           __syncwarp();   // every lane holds its scores: one arrival per warp
           if (lane == 0) mbar_arrive(&sh.s_free[buf]);
+          TRACE((tid & 127) == 0 && half == 0, 1, kt, 6, trace_clock());
           if (kt * 128 + 127 > tile_jlim) {
             const int climit = jlim - kt * 128 - c0;
 #pragma unroll
@@ -455,177 +523,255 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           }
           const float tm = fmaxf(m0, m1);
           mrow = fmaxf(mrow, tm);
-          const bool near_max = tm > -INFINITY && (mrow - tm) * c1 < 1.f;
+          rmx[quad * 128 + row] = mrow;
+          const float msh = fmaxf(fmaxf(rmx[row], rmx[128 + row]), fmaxf(rmx[256 + row], rmx[384 + row]));
+          const bool near_max = tm > -INFINITY && (msh - tm) * c1 < 1.f;
           mark_bits |= (near_max ? 1u : 0u) << (kt & 31);
+          if (!lovf) {
+            if (lw > lstop) {
+              lovf = true;
+            } else {
+              // masked entries are -inf and never pass; one predicated store and pointer bump each
+              const float thr = msh - inv_c1;
+#pragma unroll
+              for (int x = 0; x < 64; ++x)
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "setp.gt.f32 p, %1, %2;\n\t"
+                    "@p st.global.f32 [%0], %1;\n\t"
+                    "@p add.u64 %0, %0, 2048;\n\t}"
+                    : "+l"(lw)
+                    : "f"(__uint_as_float(r[x])), "f"(thr)
+                    : "memory");
+            }
+          }
+          TRACE((tid & 127) == 0 && half == 0, 1, kt, 7, trace_clock());
         });
         publish_marks();
         sh.part[quad][0][row] = mrow;
         named_bar_sync(1, kFwdRowThreads);
         float m = fmaxf(fmaxf(sh.part[0][0][row], sh.part[1][0][row]), fmaxf(sh.part[2][0][row], sh.part[3][0][row]));
         if (warp == 0) {
-          // tiles of the first threshold pass (all of them if nothing was marked: non-finite scores)
+          // tiles of the next pass (all of them if nothing was marked: non-finite scores)
           const int lo_t = lane * 32;
           const uint32_t full = nkt >= lo_t + 32 ? 0xffffffffu : (nkt > lo_t ? (1u << (nkt - lo_t)) - 1u : 0u);
           uint32_t nx = ((volatile uint32_t*)sh.act_next)[lane];
-          if (!__any_sync(0xffffffffu, nx != 0u) || (p.debug & 256)) nx = full;
+          if (!__any_sync(0xffffffffu, nx != 0u) || FLA_DBG(p, 256)) nx = full;
           sh.act[1][lane] = nx;
           sh.act_next[lane] = 0u;
         }
-        named_bar_sync(2, kFwdRowThreads);
+        const bool use_list = named_bar_and(2, kFwdRowThreads, !lovf);
         m = live ? m * c1 : 0.f;
         const float n = (float)(jlim + 1);
         float ts = -1.f, lo = -1.f, hi = live ? -exp2f(-(p.alpha - 1.f) * log2f(fmaxf(n, 1.f))) : -1.f;
         bool done = !live || n <= 1.f;
-        bool cont = p.niter > 0;
-        signal_pass(cont);
-        rpass = 1;
-        for (int it = 0; cont; ++it) {
-          float a0 = 0.f, a1 = 0.f, a2 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f;
-          const float off = m + ts;   // d = X - tau with X = s*c1
-          // tiles with an entry above tau, collected per 32-tile word and published once per word
-          uint32_t hit_bits = 0;
-          int hit_word = 0;
-          auto publish_hits = [&]() {
-            const uint32_t any = __reduce_or_sync(0xffffffffu, hit_bits);
-            if (any != 0u && lane == 0) atomicOr(&sh.act_next[hit_word], any);
-            hit_bits = 0;
-          };
-          // The two groups take turns at the arithmetic: a group sums its tile while the other
-          // one waits for its next score tile and loads it, so the floating-point pipe of a
-          // scheduler serves two warps at a time instead of four in lockstep followed by none.
-          // Barrier 4 + g is group g's "your turn"; the group owning the first tile of the pass
-          // gets the first turn from the other one, and whoever did not sum last takes the
-          // turn that is left over.
-          const uint32_t first_grp = sn & 1u;
-          int nact_pass = 0;
-          for (int w = 0; w * 32 < nkt; ++w) nact_pass += __popc(((volatile uint32_t*)sh.act[rpass & 1u])[w]);
-          if ((uint32_t)grp != first_grp) named_bar_arrive(4 + (int)first_grp, kFwdRowThreads);
-          for_my_tiles(rpass, [&](int kt, uint32_t cs) {
-            const uint32_t buf = cs & 3;
-            bool hit = false;           // some entry of this tile lies above tau
-            if ((kt >> 5) != hit_word) { publish_hits(); hit_word = kt >> 5; }
-            TRACE((tid & 127) == 0 && half == 0, rpass == 1 ? 1 : 0, kt, 4, trace_clock());
-            mbar_wait(&sh.s_full[buf], (cs >> 2) & 1, abort_flag, status, 31);
-            TRACE((tid & 127) == 0 && half == 0, rpass == 1 ? 1 : 0, kt, 5, trace_clock());
-            __syncwarp();
-            tc_fence_after_sync();
-            // this thread's half row into registers, buffer handed back at once: the next product
-            // into this buffer runs while the row is summed
-            uint32_t r[64];
-            tmem_ld64_sync(tgrp + buf * 128 + c0, r);
-            tc_fence_before_sync();
-            // the token is zero; adding it makes every sum below depend on the arrive, so the
-            // buffer is handed back before the arithmetic instead of after it
-            __syncwarp();   // every lane holds its scores: one arrival per warp
-            float noff = __uint_as_float(lane == 0 ? mbar_arrive_token(&sh.s_free[buf]) : 0u) - off;
-            const bool need_mask = kt * 128 + 127 > tile_jlim;
-            if (need_mask) {   // diagonal / sequence end: masked entries contribute nothing
-              const int climit = jlim - kt * 128 - c0;
-#pragma unroll
-              for (int x = 0; x < 64; ++x)
-                if (x > climit) r[x] = 0xff800000u;   // -inf
-            }
-            noff += __uint_as_float(named_bar_sync_token(4 + grp, kFwdRowThreads));   // my turn
-            TRACE((tid & 127) == 0 && half == 0, rpass == 1 ? 1 : 0, kt, 6, trace_clock_dep(noff, noff, noff));
-            if (KIND == 0 && !(p.debug & 1)) {
-              // alpha = 1.5: d <= 1 on the whole bracket, so one saturating fma yields max(d, 0)
-              // (and 0 for a masked entry); sums kept as packed pairs
-              uint64_t s0 = pack2(0.f, 0.f), s1 = s0, s2 = s0;
-#pragma unroll
-              for (int x = 0; x < 64; x += 2) {
-                const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, noff));
-                const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, noff));
-                const uint64_t ee = pack2(e0, e1);
-                s0 = fma2(ee, ee, s0);
-                s1 = add2(s1, ee);
-                s2 = add2(s2, pack2(e0 > 0.f ? 1.f : 0.f, e1 > 0.f ? 1.f : 0.f));
+        // One update of this row's threshold from the three sums over its support; returns true when
+        // the threshold fell by more than rounding (tile skipping relies on it not falling).
+        auto update_tau = [&](float sum0, float sum1, float sum2v, int it, float tol_halley, float tol_newton,
+                              float tol_bisect) {
+          bool regular;
+          float t = tau_update(ts, sum0, sum1, sum2v, e, lo, hi, &regular);
+          if (KIND == 0 && it == 0 && !(p.flags & FLA_FLAG_PLAIN_FIRST_STEP)) {
+            // first step of a row: the tail-model step where the moments admit it
+            const float jump = gpd_first_step(sum0, sum1, sum2v);
+            if (jump > 0.f && ts + jump > t && ts + jump <= hi) { t = ts + jump; regular = false; }
+          }
+          const float tol = regular ? (e >= 2.f ? tol_halley : tol_newton) : tol_bisect;
+          // quadratic / cubic convergence: once a step is this small the next one is far below
+          // fp32 resolution; the second term covers rows whose |tau| is too large to resolve it
+          if (fabsf(t - ts) <= fmaxf(tol, 4e-7f * fabsf(m))) done = true;
+          if (t >= ts) { ts = t; return false; }
+          if (ts - t > 2e-6f * fmaxf(1.f, fabsf(m))) { ts = t; return true; }
+          return false;
+        };
+        if (use_list) {
+          // ---- threshold iteration on the candidate lists: the producer and the issuers go straight
+          // to the last pass (tiles marked by the row-max pass) while the row threads iterate
+          signal_pass(false);
+          rpass = 1;
+          const int lcnt = (int)((lw - lbase) / kFwdRowThreads);
+          if (tid == 0 && status) atomicAdd(status + 6, 1);
+          for (int it = 0; it < p.niter; ++it) {
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f;
+            const float noff = -(m + ts);   // d = X - tau with X = s*c1
+            auto acc = [&](float sv, float& s0, float& s1, float& s2) {
+              const float d = fmaf(sv, c1, noff);
+              if (KIND == 0) {
+                const float ee = __saturatef(d);   // d <= 1 on the whole bracket
+                s0 = fmaf(ee, ee, s0); s1 += ee; s2 += d > 0.f ? 1.f : 0.f;
+              } else if (KIND == 1) {
+                s0 += fmaxf(d, 0.f); s1 += d > 0.f ? 1.f : 0.f;
+              } else if (d > 0.f) {
+                float pw, u;
+                p_and_u<2>(d, e, pw, u);
+                s0 += pw; s1 += u; s2 += __fdividef(u, d);
               }
-              const float cnt = sum2(s2);
-              a0 += sum2(s0); a1 += sum2(s1); a2 += cnt;
-              hit = cnt > 0.f;
-            } else if (!(p.debug & 1)) {
-              auto chunk_sums = [&](const uint32_t* rc) {
+            };
+            int x = 0;
+            for (; x + 8 <= lcnt; x += 8) {   // eight loads in flight per thread: the lists sit in L2
+              float vv[8];
 #pragma unroll
-                for (int x = 0; x < 32; x += 2) {
-                  const float d0 = fmaf(__uint_as_float(rc[x]), c1, noff);
-                  const float d1 = fmaf(__uint_as_float(rc[x + 1]), c1, noff);
-                  hit |= (d0 > 0.f) | (d1 > 0.f);
-                  if (KIND == 0) {
-                    const float e0 = fmaxf(d0, 0.f), e1 = fmaxf(d1, 0.f);
-                    a0 = fmaf(e0, e0, a0); a1 += e0; a2 += d0 > 0.f ? 1.f : 0.f;
-                    b0 = fmaf(e1, e1, b0); b1 += e1; b2 += d1 > 0.f ? 1.f : 0.f;
-                  } else if (KIND == 1) {
-                    a0 += fmaxf(d0, 0.f); a1 += d0 > 0.f ? 1.f : 0.f;
-                    b0 += fmaxf(d1, 0.f); b1 += d1 > 0.f ? 1.f : 0.f;
-                  } else {
-                    if (d0 > 0.f) { float pw, u; p_and_u<2>(d0, e, pw, u); a0 += pw; a1 += u; a2 += __fdividef(u, d0); }
-                    if (d1 > 0.f) { float pw, u; p_and_u<2>(d1, e, pw, u); b0 += pw; b1 += u; b2 += __fdividef(u, d1); }
-                  }
-                }
-              };
-              chunk_sums(r);
-              chunk_sums(r + 32);
-            } else {
-              a0 += __uint_as_float(r[0] ^ r[37] ^ r[63]);
-              hit = true;
+              for (int y = 0; y < 8; ++y) vv[y] = __ldcg(lbase + (size_t)(x + y) * kFwdRowThreads);
+#pragma unroll
+              for (int y = 0; y < 8; y += 2) { acc(vv[y], a0, a1, a2); acc(vv[y + 1], b0, b1, b2); }
             }
-            TRACE((tid & 127) == 0 && half == 0, rpass == 1 ? 1 : 0, kt, 7, trace_clock_dep(a0, a1, a2));
-            // hand the turn over once the sums are done (the sums feed the barrier's memory clobber)
-            named_bar_arrive_after(4 + (grp ^ 1), kFwdRowThreads, a0 + b0, a1 + b1, a2 + b2);
-            hit_bits |= (hit ? 1u : 0u) << (kt & 31);
-          });
-          {
-            // the group that did not sum last consumes the turn that is left over
-            const uint32_t last_grp = (first_grp + (uint32_t)nact_pass + 1u) & 1u;
-            if (nact_pass > 0 ? (uint32_t)grp != last_grp : (uint32_t)grp == first_grp) named_bar_sync(4 + grp, kFwdRowThreads);
-          }
-          publish_hits();
-          sh.part[quad][0][row] = a0 + b0;
-          sh.part[quad][1][row] = a1 + b1;
-          sh.part[quad][2][row] = a2 + b2;
-          named_bar_sync(1, kFwdRowThreads);
-          if (!done) {
-            bool regular;
-            const float sum0 = (sh.part[0][0][row] + sh.part[1][0][row]) + (sh.part[2][0][row] + sh.part[3][0][row]);
-            const float sum1 = (sh.part[0][1][row] + sh.part[1][1][row]) + (sh.part[2][1][row] + sh.part[3][1][row]);
-            const float sum2v = (sh.part[0][2][row] + sh.part[1][2][row]) + (sh.part[2][2][row] + sh.part[3][2][row]);
-            float t = tau_update(ts, sum0, sum1, sum2v, e, lo, hi, &regular);
-            if (KIND == 0 && it == 0 && !(p.debug & 128)) {
-              // first step of a row: the tail-model step where the moments admit it
-              const float jump = gpd_first_step(sum0, sum1, sum2v);
-              if (jump > 0.f && ts + jump > t && ts + jump <= hi) { t = ts + jump; regular = false; }
+            for (; x < lcnt; ++x) acc(__ldcg(lbase + (size_t)x * kFwdRowThreads), a0, a1, a2);
+            sh.part[quad][0][row] = a0 + b0;
+            sh.part[quad][1][row] = a1 + b1;
+            sh.part[quad][2][row] = a2 + b2;
+            named_bar_sync(1, kFwdRowThreads);
+            if (!done) {
+              const float sum0 = (sh.part[0][0][row] + sh.part[1][0][row]) + (sh.part[2][0][row] + sh.part[3][0][row]);
+              const float sum1 = (sh.part[0][1][row] + sh.part[1][1][row]) + (sh.part[2][1][row] + sh.part[3][1][row]);
+              const float sum2v = (sh.part[0][2][row] + sh.part[1][2][row]) + (sh.part[2][2][row] + sh.part[3][2][row]);
+              // an iteration costs a few thousand cycles here, not a pass over the keys: converge
+              update_tau(sum0, sum1, sum2v, it, kListTolHalley, kListTolNewton, kListTol);
             }
-            const float tol = regular ? (e >= 2.f ? kTauTolHalley : kTauTolNewton) : kTauTol;
-            // quadratic / cubic convergence: once a step is this small the next one is far below
-            // fp32 resolution; the second term covers rows whose |tau| is too large to resolve it
-            if (fabsf(t - ts) <= fmaxf(tol, 4e-7f * fabsf(m))) done = true;
-            // Tile skipping relies on tau not falling.  A fall within rounding is dropped; a real
-            // one (after a first step that overshot, or a bisection) makes the next pass visit the
-            // tiles of the first threshold pass again: tau never leaves the bracket, whose lower
-            // end is where that pass evaluated.
-            if (t >= ts) ts = t;
-            else if (ts - t > 2e-6f * fmaxf(1.f, fabsf(m))) { ts = t; *(volatile int*)&sh.force_all = 1; }
+            // (the barrier also orders this iteration's reads of the partial sums before the next writes)
+            if (named_bar_and(2, kFwdRowThreads, done || *abort_flag != 0)) break;
           }
-          const bool all_done = named_bar_and(2, kFwdRowThreads, done);
-          cont = !all_done && (it + 1 < p.niter) && !*abort_flag;
-          if (p.debug & 4) cont = it + 1 < 5;
-          if (warp == 0) {
-            // tiles of the next pass: those in which some row found an entry above its tau
-            const int lo_t = lane * 32;
-            const uint32_t full = nkt >= lo_t + 32 ? 0xffffffffu : (nkt > lo_t ? (1u << (nkt - lo_t)) - 1u : 0u);
-            uint32_t nx = ((volatile uint32_t*)sh.act_next)[lane];
-            const bool none = !__any_sync(0xffffffffu, nx != 0u);   // only with non-finite scores
-            if (it == 0) sh.act_base[lane] = none ? full : nx;
-            if (none) nx = full;
-            if (*(volatile int*)&sh.force_all) nx = sh.act_base[lane];   // some tau fell in this step
-            sh.act[(rpass + 1u) & 1u][lane] = nx;
-            sh.act_next[lane] = 0u;
-            __syncwarp();
-            if (lane == 0) *(volatile int*)&sh.force_all = 0;
-          }
-          named_bar_sync(3, kFwdRowThreads);
-          ++rpass;
+          TRACE_PASS(29);
+        } else {
+          if (tid == 0 && status) atomicAdd(status + 7, 1);
+          bool cont = p.niter > 0;
           signal_pass(cont);
+          rpass = 1;
+          for (int it = 0; cont; ++it) {
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f;
+            const float off = m + ts;   // d = X - tau with X = s*c1
+            // tiles with an entry above tau, collected per 32-tile word and published once per word
+            uint32_t hit_bits = 0;
+            int hit_word = 0;
+            auto publish_hits = [&]() {
+              const uint32_t any = __reduce_or_sync(0xffffffffu, hit_bits);
+              if (any != 0u && lane == 0) atomicOr(&sh.act_next[hit_word], any);
+              hit_bits = 0;
+            };
+            // The two groups take turns at the arithmetic: a group sums its tile while the other
+            // one waits for its next score tile and loads it, so the floating-point pipe of a
+            // scheduler serves two warps at a time instead of four in lockstep followed by none.
+            // Barrier 4 + g is group g's "your turn"; the group owning the first tile of the pass
+            // gets the first turn from the other one, and whoever did not sum last takes the
+            // turn that is left over.
+            const uint32_t first_grp = sn & 1u;
+            int nact_pass = 0;
+            for (int w = 0; w * 32 < nkt; ++w) nact_pass += __popc(((volatile uint32_t*)sh.act[rpass & 1u])[w]);
+            if ((uint32_t)grp != first_grp) named_bar_arrive(4 + (int)first_grp, kFwdRowThreads);
+            for_my_tiles(rpass, [&](int kt, uint32_t cs) {
+              const uint32_t buf = cs & 3;
+              bool hit = false;           // some entry of this tile lies above tau
+              if ((kt >> 5) != hit_word) { publish_hits(); hit_word = kt >> 5; }
+              TRACE((tid & 127) == 0 && half == 0, 0, kt, 4, trace_clock());
+              mbar_wait(&sh.s_full[buf], (cs >> 2) & 1, abort_flag, status, 31);
+              TRACE((tid & 127) == 0 && half == 0, 0, kt, 5, trace_clock());
+              __syncwarp();
+              tc_fence_after_sync();
+              // this thread's half row into registers, buffer handed back at once: the next product
+              // into this buffer runs while the row is summed
+              uint32_t r[64];
+              tmem_ld64_sync(tgrp + buf * 128 + c0, r);
+              tc_fence_before_sync();
+              // the token is zero; adding it makes every sum below depend on the arrive, so the
+              // buffer is handed back before the arithmetic instead of after it
+              __syncwarp();   // every lane holds its scores: one arrival per warp
+              float noff = __uint_as_float(lane == 0 ? mbar_arrive_token(&sh.s_free[buf]) : 0u) - off;
+              const bool need_mask = kt * 128 + 127 > tile_jlim;
+              if (need_mask) {   // diagonal / sequence end: masked entries contribute nothing
+                const int climit = jlim - kt * 128 - c0;
+  #pragma unroll
+                for (int x = 0; x < 64; ++x)
+                  if (x > climit) r[x] = 0xff800000u;   // -inf
+              }
+              noff += __uint_as_float(named_bar_sync_token(4 + grp, kFwdRowThreads));   // my turn
+              TRACE((tid & 127) == 0 && half == 0, 0, kt, 6, trace_clock_dep(noff, noff, noff));
+              if (KIND == 0 && !FLA_DBG(p, 1)) {
+                // alpha = 1.5: d <= 1 on the whole bracket, so one saturating fma yields max(d, 0)
+                // (and 0 for a masked entry); sums kept as packed pairs
+                uint64_t s0 = pack2(0.f, 0.f), s1 = s0, s2 = s0;
+  #pragma unroll
+                for (int x = 0; x < 64; x += 2) {
+                  const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, noff));
+                  const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, noff));
+                  const uint64_t ee = pack2(e0, e1);
+                  s0 = fma2(ee, ee, s0);
+                  s1 = add2(s1, ee);
+                  s2 = add2(s2, pack2(e0 > 0.f ? 1.f : 0.f, e1 > 0.f ? 1.f : 0.f));
+                }
+                const float cnt = sum2(s2);
+                a0 += sum2(s0); a1 += sum2(s1); a2 += cnt;
+                hit = cnt > 0.f;
+              } else if (!FLA_DBG(p, 1)) {
+                auto chunk_sums = [&](const uint32_t* rc) {
+  #pragma unroll
+                  for (int x = 0; x < 32; x += 2) {
+                    const float d0 = fmaf(__uint_as_float(rc[x]), c1, noff);
+                    const float d1 = fmaf(__uint_as_float(rc[x + 1]), c1, noff);
+                    hit |= (d0 > 0.f) | (d1 > 0.f);
+                    if (KIND == 0) {
+                      const float e0 = fmaxf(d0, 0.f), e1 = fmaxf(d1, 0.f);
+                      a0 = fmaf(e0, e0, a0); a1 += e0; a2 += d0 > 0.f ? 1.f : 0.f;
+                      b0 = fmaf(e1, e1, b0); b1 += e1; b2 += d1 > 0.f ? 1.f : 0.f;
+                    } else if (KIND == 1) {
+                      a0 += fmaxf(d0, 0.f); a1 += d0 > 0.f ? 1.f : 0.f;
+                      b0 += fmaxf(d1, 0.f); b1 += d1 > 0.f ? 1.f : 0.f;
+                    } else {
+                      if (d0 > 0.f) { float pw, u; p_and_u<2>(d0, e, pw, u); a0 += pw; a1 += u; a2 += __fdividef(u, d0); }
+                      if (d1 > 0.f) { float pw, u; p_and_u<2>(d1, e, pw, u); b0 += pw; b1 += u; b2 += __fdividef(u, d1); }
+                    }
+                  }
+                };
+                chunk_sums(r);
+                chunk_sums(r + 32);
+              } else {
+                a0 += __uint_as_float(r[0] ^ r[37] ^ r[63]);
+                hit = true;
+              }
+              TRACE((tid & 127) == 0 && half == 0, 0, kt, 7, trace_clock_dep(a0, a1, a2));
+              // hand the turn over once the sums are done (the sums feed the barrier's memory clobber)
+              named_bar_arrive_after(4 + (grp ^ 1), kFwdRowThreads, a0 + b0, a1 + b1, a2 + b2);
+              hit_bits |= (hit ? 1u : 0u) << (kt & 31);
+            });
+            {
+              // the group that did not sum last consumes the turn that is left over
+              const uint32_t last_grp = (first_grp + (uint32_t)nact_pass + 1u) & 1u;
+              if (nact_pass > 0 ? (uint32_t)grp != last_grp : (uint32_t)grp == first_grp) named_bar_sync(4 + grp, kFwdRowThreads);
+            }
+            publish_hits();
+            sh.part[quad][0][row] = a0 + b0;
+            sh.part[quad][1][row] = a1 + b1;
+            sh.part[quad][2][row] = a2 + b2;
+            named_bar_sync(1, kFwdRowThreads);
+            if (!done) {
+              const float sum0 = (sh.part[0][0][row] + sh.part[1][0][row]) + (sh.part[2][0][row] + sh.part[3][0][row]);
+              const float sum1 = (sh.part[0][1][row] + sh.part[1][1][row]) + (sh.part[2][1][row] + sh.part[3][1][row]);
+              const float sum2v = (sh.part[0][2][row] + sh.part[1][2][row]) + (sh.part[2][2][row] + sh.part[3][2][row]);
+              // Tile skipping relies on tau not falling.  A fall within rounding is dropped; a real
+              // one (after a first step that overshot, or a bisection) makes the next pass visit the
+              // tiles of the first threshold pass again: tau never leaves the bracket, whose lower
+              // end is where that pass evaluated.
+              if (update_tau(sum0, sum1, sum2v, it, kTauTolHalley, kTauTolNewton, kTauTol)) *(volatile int*)&sh.force_all = 1;
+            }
+            const bool all_done = named_bar_and(2, kFwdRowThreads, done);
+            cont = !all_done && (it + 1 < p.niter) && !*abort_flag;
+            if (FLA_DBG(p, 4)) cont = it + 1 < 5;
+            if (warp == 0) {
+              // tiles of the next pass: those in which some row found an entry above its tau
+              const int lo_t = lane * 32;
+              const uint32_t full = nkt >= lo_t + 32 ? 0xffffffffu : (nkt > lo_t ? (1u << (nkt - lo_t)) - 1u : 0u);
+              uint32_t nx = ((volatile uint32_t*)sh.act_next)[lane];
+              const bool none = !__any_sync(0xffffffffu, nx != 0u);   // only with non-finite scores
+              if (it == 0) sh.act_base[lane] = none ? full : nx;
+              if (none) nx = full;
+              if (*(volatile int*)&sh.force_all) nx = sh.act_base[lane];   // some tau fell in this step
+              sh.act[(rpass + 1u) & 1u][lane] = nx;
+              sh.act_next[lane] = 0u;
+              __syncwarp();
+              if (lane == 0) *(volatile int*)&sh.force_all = 0;
+            }
+            named_bar_sync(3, kFwdRowThreads);
+            ++rpass;
+            signal_pass(cont);
+          }
         }
         rstat = m + ts;
       } else {

@@ -81,8 +81,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // that is not taken.  The threads that issue copies and products execute two such waits per
 // tile, strictly in sequence with everything else they do.
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                   int* status, int tag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+                                                   int* status, int tag, uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (i > 2048) __nanosleep(64);
@@ -96,9 +96,9 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
   return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int tag) {
+                                          int* status, int tag, uint32_t limit = kSpinLimit) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, status, tag);
+  return mbar_wait_slow(bar, parity, abort_flag, status, tag, limit);
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -34,7 +34,11 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
 
-  if (tid == 0) {
+  // variant 3: nothing is copied and nothing issued, so the first wait below runs out after a short
+  // spin limit; the kernel then takes the same way out as the attention kernels after an expired
+  // wait: error words written, every later wait returns at once, tensor memory freed, normal return.
+  const uint32_t limit = variant == 3 ? (1u << 12) : kSpinLimit;
+  if (tid == 0 && variant != 3) {
     mbar_expect_tx(&bar_full, 2 * ST_TILE_BYTES);
     tma_load_4d(sA, &map_a, &bar_full, 0, 0, 0, 0);
     tma_load_4d(sA + ST_TILE_BYTES / 2, &map_a, &bar_full, 64, 0, 0, 0);
@@ -57,11 +61,11 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     }
     tmem_st_wait();
   }
-  mbar_wait(&bar_full, 0, &abort_flag, status, 1);
+  mbar_wait(&bar_full, 0, &abort_flag, status, 1, limit);
   tc_fence_before_sync();
   __syncthreads();
 
-  if (tid == 0) {
+  if (tid == 0 && variant != 3) {
     tc_fence_after_sync();
     const uint32_t a_addr = smem_u32(sA), b_addr = smem_u32(sB);
     if (variant == 0 || variant == 2) {
@@ -83,7 +87,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     }
     umma_commit(&bar_mma);
   }
-  mbar_wait(&bar_mma, 0, &abort_flag, status, 2);
+  mbar_wait(&bar_mma, 0, &abort_flag, status, 2, limit);
   tc_fence_after_sync();
 #pragma unroll
   for (int ch = 0; ch < 4; ++ch) {
@@ -91,7 +95,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     tmem_ld32(tmem_base + lane_base + ch * 32, r);
     tmem_ld_wait();
 #pragma unroll
-    for (int x = 0; x < 32; ++x) c[(size_t)tid * 128 + ch * 32 + x] = __uint_as_float(r[x]);
+    for (int x = 0; x < 32; ++x) c[(size_t)tid * 128 + ch * 32 + x] = variant == 3 ? 0.f : __uint_as_float(r[x]);
   }
   tc_fence_before_sync();
   __syncthreads();

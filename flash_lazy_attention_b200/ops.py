@@ -25,6 +25,13 @@ _DTYPES = {torch.float32: _lib.FLA_F32, torch.float16: _lib.FLA_F16, torch.bfloa
 # FLA_PATH=simt|tcgen05 pins the kernel family (testing); default lets the library choose.
 _PATH_ENV = {"": _lib.PATH_AUTO, "auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}
 _forced_path = None
+_flags = 0
+
+
+def set_flags(flags: int) -> None:
+    """fla_attn_geom.flags for the calls that follow (``_lib.FLAG_*``; 0 restores normal operation)."""
+    global _flags
+    _flags = int(flags)
 
 
 def set_path(name: str | None) -> None:
@@ -88,14 +95,18 @@ def read_status(device=None, reset: bool = False) -> dict:
     if reset:
         buf.zero_()
     return {"error": vals[0], "wait_tag": vals[1], "block": vals[2],
-            "tile_mmas": (vals[4] & 0xFFFFFFFF) | ((vals[5] & 0xFFFFFFFF) << 32)}
+            "tile_mmas": (vals[4] & 0xFFFFFFFF) | ((vals[5] & 0xFFFFFFFF) << 32),
+            "list_ctas": vals[6], "pass_ctas": vals[7]}
 
 
 def check_status(device=None) -> None:
-    """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
-    st = read_status(device)
-    if st["error"]:
-        raise RuntimeError(f"device wait expired in a tensor-core kernel: {st}")
+    """Raise if a kernel reported that one of its bounded waits ran out (fla_check_status: waits
+    for the device's current stream)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    buf = _status_buf(device)
+    with torch.cuda.device(device):
+        rc = _lib.load().fla_check_status(buf.data_ptr(), torch.cuda.current_stream(device).cuda_stream)
+    _lib.check(rc, "fla_check_status")
 
 
 def _geom(q: torch.Tensor, causal: bool, varlen32) -> AttnGeom:
@@ -107,7 +118,14 @@ def _geom(q: torch.Tensor, causal: bool, varlen32) -> AttnGeom:
     g.varlen = varlen32.data_ptr() if varlen32 is not None else None
     g.path = _path()
     g.status = _status_buf(q.device).data_ptr()
+    g.flags = _flags
     return g
+
+
+def _fwd_workspace(lib, g, device):
+    """Scratch of the tensor-core forward (candidate lists); None when it has no use for any."""
+    nbytes = lib.fla_entmax_attn_fwd_workspace(g)
+    return torch.empty((nbytes,), dtype=torch.uint8, device=device) if nbytes else None
 
 
 def _varlen32(varlen, q):
@@ -154,10 +172,13 @@ class EntmaxAttnFunc(torch.autograd.Function):
             if use_block_mask:
                 words = lib.fla_block_mask_words(L)
                 mask = torch.empty((B, H, (L + 127) // 128, words), dtype=torch.int32, device=q.device)
+            ws = _fwd_workspace(lib, g, q.device)
             rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), float(alpha), int(niter),
                                          tau.data_ptr(), aux_o.data_ptr() if need_aux else None,
                                          aux_s.data_ptr() if need_aux else None,
-                                         mask.data_ptr() if mask is not None else None, _stream(q))
+                                         mask.data_ptr() if mask is not None else None,
+                                         ws.data_ptr() if ws is not None else None,
+                                         ws.numel() if ws is not None else 0, _stream(q))
             _lib.check(rc, "fla_entmax_attn_fwd")
         ctx.save_for_backward(q, k, v, tau, aux_o, aux_s, mask, vl)
         ctx.alpha, ctx.is_causal = float(alpha), bool(is_causal)
@@ -211,10 +232,14 @@ def entmax_attention_forward(q, k, v, alpha=1.5, niter=10, is_causal=False, varl
         if use_block_mask:
             mask = torch.empty((B, H, (L + 127) // 128, lib.fla_block_mask_words(L)), dtype=torch.int32,
                                device=q.device)
-        rc = lib.fla_entmax_attn_fwd(_geom(q, is_causal, vl), _t4(q), _t4(k), _t4(v), _t4(out), float(alpha),
+        g = _geom(q, is_causal, vl)
+        ws = _fwd_workspace(lib, g, q.device)
+        rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), float(alpha),
                                      int(niter), tau.data_ptr(), aux_o.data_ptr() if need_aux else None,
                                      aux_s.data_ptr() if need_aux else None,
-                                     mask.data_ptr() if mask is not None else None, _stream(q))
+                                     mask.data_ptr() if mask is not None else None,
+                                     ws.data_ptr() if ws is not None else None,
+                                     ws.numel() if ws is not None else 0, _stream(q))
         _lib.check(rc, "fla_entmax_attn_fwd")
     return out, tau, aux_o, aux_s, mask
 

@@ -10,7 +10,9 @@
  *   - nothing is thrown, no device memory is allocated, nothing synchronises the
  *     device, the current device is never changed: the caller owns every buffer
  *     (outputs, saved statistics, workspaces) and passes the cudaStream_t to
- *     enqueue on (as a void*; NULL is the legacy default stream);
+ *     enqueue on (as a void*; NULL is the legacy default stream).  Two documented
+ *     exceptions: fla_entmax_attn_bwd_static keeps its scratch inside the library,
+ *     and fla_check_status waits for the stream it is given;
  *   - all pointers are device pointers of the device that is current in the
  *     calling thread, except the POD descriptor structs, which are host memory;
  *   - attention tensors are [B,H,L,D] views described by element strides; the
@@ -42,6 +44,14 @@ extern "C" {
 #define FLA_PATH_SIMT 1     /* fp32 CUDA-core kernels: any dtype, any D <= 128               */
 #define FLA_PATH_TCGEN05 2  /* tcgen05 + TMEM + TMA kernels: bf16/fp16, D in {64,128}        */
 
+/* fla_attn_geom.flags (a sum of bits; 0 in normal use).  Both change how the tensor-core
+ * forward of entmax attention finds the row thresholds, not what it computes; tests use them to
+ * reach every code path.                                                                       */
+#define FLA_FLAG_NO_CANDIDATE_LIST 1  /* iterate the thresholds by passes over recomputed score  *
+                                       * tiles even when a candidate-list workspace is given     */
+#define FLA_FLAG_PLAIN_FIRST_STEP 2   /* alpha = 1.5: plain Halley first step instead of the      *
+                                       * tail-model step                                         */
+
 /* A strided [B,H,L,D] view; strides in elements, stride[3] must be 1. */
 typedef struct fla_tensor4 {
   void* ptr;
@@ -58,8 +68,11 @@ typedef struct fla_attn_geom {
   int32_t* status;        /* device int32[8] or NULL.  Tensor-core kernels report here:        *
                            * [0] != 0: a bounded wait ran out ([1] which wait, [2] which block); *
                            * [4],[5]: low/high word of a running count of 128x128xD tile         *
-                           * products issued (the "executed FLOPs" figure).  Never cleared by    *
-                           * the library; the caller zeroes it.                                  */
+                           * products issued (the "executed FLOPs" figure); [6],[7]: forward     *
+                           * CTAs that iterated the thresholds on candidate lists / by passes     *
+                           * over score tiles.  Never cleared by the library; the caller zeroes   *
+                           * it.                                                                  */
+  int32_t flags;          /* FLA_FLAG_*                                                         */
 } fla_attn_geom;
 
 /* Library / ABI version (major*1000 + minor). */
@@ -70,6 +83,13 @@ const char* fla_last_error(void);
 
 /* 0 when `device` is a compute-capability 10.x GPU this library has code for. */
 int fla_device_supported(int device);
+
+/* Waits for `stream` and reads the status words a tensor-core kernel reports into
+ * (fla_attn_geom.status, device int32[8]).  Returns FLA_ERR_DEVICE, with the wait and the block
+ * in fla_last_error(), if a bounded wait of a kernel ran out since the words were last cleared:
+ * the results of that launch are not valid.  FLA_OK otherwise.  The only entry point that
+ * synchronises; callers that never call it pay nothing.                                       */
+int fla_check_status(const int32_t* status, void* stream);
 
 /* Which kernel family the last attention call of the calling thread used (FLA_PATH_*). */
 int fla_last_path(void);
@@ -108,7 +128,15 @@ int64_t fla_block_mask_words(int32_t L);
 int fla_entmax_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_tensor4* k,
                         const fla_tensor4* v, const fla_tensor4* o, float alpha, int niter,
                         float* tau, float* aux_o, float* aux_s, uint32_t* block_mask,
-                        void* stream);
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of scratch the forward can use for this geometry on the current device (0 when it has
+ * no use for any).  workspace (256-byte aligned) may be NULL or smaller: the tensor-core forward
+ * then finds the thresholds by repeated passes over recomputed score tiles, which is slower, with
+ * the same results.  With the workspace every row thread keeps the few percent of its scores that
+ * can lie above the threshold in a list (one slot of lists per SM) and iterates on those; contents
+ * are scratch, nothing needs clearing, and two forwards that overlap on the GPU must not share it. */
+size_t fla_entmax_attn_fwd_workspace(const fla_attn_geom* g);
 
 /* Bytes of caller-provided scratch the backward needs for this geometry. */
 size_t fla_entmax_attn_bwd_workspace(const fla_attn_geom* g);
@@ -179,7 +207,13 @@ int fla_lazy_attn_bwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_te
  *   0: C = A . B^T, A and B K-major in shared memory (TMA, 128-byte swizzle)
  *   1: C = A . B,   B stored [K][N] (MN-major in shared memory)
  *   2: C = A . B^T, A read from tensor memory
- * status: device int32[4] diagnostics, status[0] != 0 if a bounded wait ran out.          */
+ *   3: no product at all: the kernel waits, with a spin limit of a few thousand polls, on a
+ *      barrier nothing arrives on, and leaves the way every kernel of this library leaves after
+ *      an expired wait (status words set, tensor memory freed, normal return; C is zeroed).
+ *      fla_check_status(status, stream) then reports FLA_ERR_DEVICE.  It exists so that this
+ *      exit can be exercised without provoking a fault.
+ * status: device int32[4] diagnostics, cleared by the call; status[0] != 0 if a bounded wait
+ * ran out.                                                                                */
 int fla_selftest_umma(const void* a, const void* b, float* c, int variant, int32_t* status,
                       void* stream);
 

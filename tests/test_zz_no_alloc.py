@@ -29,7 +29,7 @@ def _forward(lib, q, k, v, alpha, causal, use_tc):
         aux_s = torch.empty((B, H, L), dtype=torch.float32, device=q.device)
     rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), alpha, 10, tau.data_ptr(),
                                  aux_o.data_ptr() if aux_o is not None else None,
-                                 aux_s.data_ptr() if aux_s is not None else None, None, _stream(q))
+                                 aux_s.data_ptr() if aux_s is not None else None, None, None, 0, _stream(q))
     _lib.check(rc, "fla_entmax_attn_fwd")
     return g, tau, aux_o, aux_s
 
@@ -54,13 +54,39 @@ def test_static_scratch_backward_matches_workspace_backward(dtype, D):
         _lib.check(rc, "fla_entmax_attn_bwd")
 
         got = [torch.full_like(q, float("nan")) for _ in range(3)]
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.fla_entmax_attn_bwd_static(g, _t4(q), _t4(k), _t4(v), _t4(do), alpha, tau.data_ptr(), ao, as_,
                                             None, _t4(got[0]), _t4(got[1]), _t4(got[2]), _stream(q))
         _lib.check(rc, "fla_entmax_attn_bwd_static")
         torch.cuda.synchronize()
+        if call > 0:   # the array's address was looked up by the first call: this one may not take any device memory
+            assert torch.cuda.mem_get_info()[0] == free_before
         for name, a, b in zip(("dq", "dk", "dv"), got, ref):
             assert torch.isfinite(a).all(), name
             assert close(a, b, dtype, atol32=1e-4), (name, call, float((a.float() - b.float()).abs().max()))
+
+
+def test_static_scratch_accepts_exactly_the_limit():
+    """B*H*L equal to the limit runs (one more row is refused, see below)."""
+    lib = _lib.load()
+    B, H, L, D, dtype = 128, 64, 128, 64, torch.bfloat16
+    assert B * H * L == lib.fla_entmax_attn_bwd_static_max_rows()
+    q, k, v, do = (randn((B, H, L, D), dtype, s) for s in (1, 2, 3, 4))
+    g, tau, _, _ = _forward(lib, q, k, v, 1.5, True, True)
+    ref = [torch.empty_like(q) for _ in range(3)]
+    nbytes = lib.fla_entmax_attn_bwd_workspace(g)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    _lib.check(lib.fla_entmax_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(do), 1.5, tau.data_ptr(), None, None, None,
+                                       _t4(ref[0]), _t4(ref[1]), _t4(ref[2]), ws.data_ptr(), nbytes, _stream(q)),
+               "fla_entmax_attn_bwd")
+    got = [torch.empty_like(q) for _ in range(3)]
+    _lib.check(lib.fla_entmax_attn_bwd_static(g, _t4(q), _t4(k), _t4(v), _t4(do), 1.5, tau.data_ptr(), None, None,
+                                              None, _t4(got[0]), _t4(got[1]), _t4(got[2]), _stream(q)),
+               "fla_entmax_attn_bwd_static")
+    torch.cuda.synchronize()
+    for a, b in zip(got, ref):
+        assert torch.equal(a, b)
 
 
 def test_static_scratch_rejects_oversized_problems():
