@@ -9,9 +9,12 @@ F = 3.5 * 4 * H * D * sum_b L_b^2 * c  (c = 0.5 causal), no credit for tau itera
   value      inputs resident in HBM, K steps between CUDA events, max over ranks
   e2e        the same step through the operator API from pinned HOST buffers: every step copies
              q, k, v, dO host->device and out, dq, dk, dv device->host inside the timed region
-  roofline   dominant kernel against the measured bf16 tensor peak (MEASURED_PEAKS.json)
+  roofline   the step against the measured bf16 tensor peak (MEASURED_PEAKS.json); `kernels` holds the
+             duration every library kernel clocked for itself (GPU global timer, first CTA start to last
+             CTA end) and names the dominant one
   cpu_baseline  the dense PyTorch CPU path (oracle port: scores -> 10-step bisection entmax -> PV,
-             Jacobian backward) timed on the host cores on a bounded sample, rank 0, N=1 only
+             Jacobian backward) timed on the host cores on one (batch, head) pair of the same workload,
+             rank 0, N=1 only; `config1` beside it is BASELINE.json's CPU configuration timed exactly
 
 Multi-GPU: one process per GPU (torchrun), every rank runs the per-GPU workload on its own
 (batch, head) shard; there is no collective on the data path ("weak" scaling).
@@ -66,8 +69,9 @@ class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, gpu_id: str):
+        # nvidia-smi orders GPUs by PCI bus and ignores CUDA_VISIBLE_DEVICES: select by UUID
+        self.index, self.rows, self.proc = gpu_id, [], None
 
     def __enter__(self):
         try:
@@ -96,43 +100,55 @@ class ClockSampler:
 
     def summary(self):
         if not self.rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"], "gpu": self.index}
         sm = [int(r[0]) for r in self.rows]
         busy = [x for x in sm if x > 0.5 * max(sm)] or sm
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": statistics.median(busy), "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons,
-                "samples": len(sm)}
+                "samples": len(sm), "gpu": self.index}
 
 
-def cpu_reference(L, D, alpha, causal, steps, warmup, threads=None):
-    """Times the dense CPU path on one (batch, head) pair of the workload per step."""
+def cpu_reference(L, D, alpha, causal, steps, warmup, threads=None, B=1, H=1, median=False):
+    """Times the dense CPU path on [B,H,L,D] fp32 (default: one (batch, head) pair) per step; returns
+    (dense-equivalent TFLOP/s, seconds per step, threads)."""
     import torch
     from oracle import cpu_reference_fwd_bwd
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
-    q, k, v, do = (torch.randn(1, 1, L, D, generator=g) for _ in range(4))
+    q, k, v, do = (torch.randn(B, H, L, D, generator=g) for _ in range(4))
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
         cpu_reference_fwd_bwd(q, k, v, do, alpha=alpha, is_causal=causal, n_iter=10)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
-    sec = sum(times) / len(times)
-    return 3.5 * flops_fwd(1, 1, L, D, causal) / sec / 1e12, sec, threads
+    sec = statistics.median(times) if median else sum(times) / len(times)
+    return 3.5 * flops_fwd(B, H, L, D, causal) / sec / 1e12, sec, threads
+
+
+def cpu_config1():
+    """BASELINE.json's CPU configuration, exactly: B=1 H=8 L=128 D=64 fp32, causal, alpha=1.5, bisection
+    n_iter=10, forward + backward w.r.t. q, k, v; 3 warm-ups, median of 50."""
+    tf, sec, threads = cpu_reference(128, 64, 1.5, True, 50, 3, B=1, H=8, median=True)
+    return {"workload": "B=1 H=8 L=128 D=64 fp32 causal alpha=1.5 bisection n_iter=10, fwd+bwd", "ms": sec * 1e3,
+            "gflops": tf * 1e3, "cores": threads, "statistic": "median of 50 after 3 warm-ups"}
 
 
 def run_reference(args):
+    """The reference arm: the dense CPU path (oracle port; the reference's own entmax kernels are not in its
+    checkout) on the host cores.  Every step is ONE (batch, head) pair of the workload at its full length;
+    exactly --warmup untimed and --steps timed steps are run."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     B, H, L, D, alpha, causal = WORKLOADS[args.workload]
     alpha = 1.5 if alpha is None else alpha
-    # bounded sample: the CPU path is O(L^2) memory per pair; cap the row length so a step stays in seconds
     Ls = min(L, args.cpu_len)
-    tf, sec, threads = cpu_reference(Ls, D, alpha, causal, max(1, min(args.steps, 3)), min(args.warmup, 1))
-    sample = f"1 of {B * H} (batch, head) pairs per step at L={Ls}, fp32, dense bisection n_iter=10 + Jacobian backward"
+    tf, sec, threads = cpu_reference(Ls, D, alpha, causal, args.steps, args.warmup)
+    sample = (f"1 of {B * H} (batch, head) pairs per step at L={Ls}, fp32, dense bisection n_iter=10 + Jacobian backward; "
+              f"{args.warmup} warm-up and {args.steps} timed steps")
     line = {"metric": METRIC, "impl": "reference", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -193,7 +209,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
-    ap.add_argument("--cpu-len", type=int, default=4096, help="row length of the CPU-baseline sample")
+    ap.add_argument("--cpu-len", type=int, default=8192, help="longest row of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--alpha", type=float, default=None, help="override the workload's alpha")
@@ -294,7 +310,7 @@ def main():
     barrier()
     fla.read_status(dev, reset=True)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) as clocks:
         barrier()
         ev0.record()
         for _ in range(args.steps):
@@ -312,52 +328,69 @@ def main():
         ms = float(t.item())
     value = world * F_step / (ms * 1e-3) / 1e12
 
-    # ---- per-phase kernel timing (forward kernel alone, backward kernels alone) ----------------
-    def timed(fn, reps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    # forward and backward timed inside whole steps (events between the two halves of each step)
+    # ---- per-kernel and per-phase timing, live ----------------------------------------------------------------
+    # Phases: CUDA events between the two halves of whole steps, on the stream the library launches on.
+    # Kernels: every tensor-core kernel writes the global-timer time of its first CTA's start and its last
+    # CTA's end into the status words (one launch of each per step between two clears), so the three
+    # durations come from the same steps, without a profiler.
     reps = max(3, min(args.steps, 10))
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(reps)]
+    per_kernel = {"fwd": [], "dq": [], "dkdv": []}
     torch.cuda.synchronize()
     for ev in marks:
         q.grad = k.grad = v.grad = None
+        fla.read_status(dev, reset=True)
         ev[0].record()
         out = forward()
         ev[1].record()
         out.backward(do)
         ev[2].record()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        for name, val in fla.read_status(dev)["kernel_ms"].items():
+            if val is not None:
+                per_kernel[name].append(val)
     fwd_ms = sum(ev[0].elapsed_time(ev[1]) for ev in marks) / reps
     bwd_ms = sum(ev[1].elapsed_time(ev[2]) for ev in marks) / reps
     peak, peak_sustained, peak_kind = measured_peaks()
-    if fwd_ms >= bwd_ms:
-        dom, dom_ms, dom_flops = "forward kernel (tau passes + P.V)", fwd_ms, F_fwd
-    else:
-        dom, dom_ms, dom_flops = "backward kernels (delta row pass + dQ + dK/dV)", bwd_ms, 2.5 * F_fwd
-    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     executed = status["tile_mmas"] * 2.0 * 128 * 128 * D / max(args.steps, 1)
-    # DRAM bytes per launch of the dominant kernel(s): ncu capture of workload `mid` (profiles/), scaled by
-    # the number of (batch, head, row) units.  The grid is (batch, head)-major, so the K/V (or Q/dO) tiles that
-    # the CTAs in flight share stay in L2 at every size and the traffic grows with the tensor sizes; entmax
-    # kernels at D = 128 only.  mid: forward 100.8 MB read + 17.5 MB written; dQ kernel 134.8 + 16.9,
-    # dK/dV kernel 135.4 + 35.1.
-    traffic = None
-    if not is_lazy and D == 128 and varlen is None:
-        mid_bytes = 118.3e6 if fwd_ms >= bwd_ms else 322.2e6
-        traffic = mid_bytes * (B * H * L) / (2 * 16 * 4096)
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_sustained, "unit": "TFLOP/s",
-                "frac": achieved / peak_sustained, "traffic": traffic, "kernel": dom, "peak_kind": f"{peak_kind}, sustained",
+    # Credit per kernel in units of one masked L x L x D contraction (F_fwd / 2): the forward computes S and P.V
+    # (2); the backward is credited 5 (S, dP, dV, dK, dQ), of which S and dP are needed once for both of its
+    # kernels and are split evenly: dQ kernel 1 + 1, dK/dV kernel 2 + 1.
+    unit = F_fwd / 2.0
+    credit = {"fwd": 2.0, "dq": 2.0, "dkdv": 3.0}
+    labels = {"fwd": "forward kernel (row max + candidate lists, S, P.V)", "dq": "dQ kernel (delta sweep, S, dP, dQ)",
+              "dkdv": "dK/dV kernel (S^T, dP^T, dV, dK)"}
+    traffic_file = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    traffic_tab = {}
+    if os.path.exists(traffic_file):
+        with open(traffic_file) as fh:
+            traffic_tab = json.load(fh)
+    kernels = {}
+    for name, vals in per_kernel.items():
+        if not vals:
+            continue
+        kms = statistics.median(vals)
+        ktf = credit[name] * unit / (kms * 1e-3) / 1e12
+        kernels[name] = {"what": labels[name], "ms": kms, "credited_units": credit[name], "tflops": ktf,
+                         "frac": ktf / peak_sustained}
+        # DRAM bytes per launch: an ncu capture of a smaller workload of the same kernel, scaled by the number of
+        # (batch, head, row) units (the (batch, head)-major grid keeps shared tiles in L2, so traffic follows the
+        # tensor sizes); entmax kernels at D = 128 without varlen only
+        t = traffic_tab.get("kernels", {}).get(name)
+        if t and not is_lazy and D == 128 and varlen is None:
+            kernels[name]["traffic"] = (t["dram_read_bytes"] + t["dram_write_bytes"]) * (B * H * L) / float(traffic_tab["units"])
+    dom = max(kernels, key=lambda n: kernels[n]["ms"]) if kernels else None
+    roofline = {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s",
+                "frac": value / world / peak_sustained,
+                "traffic": sum(kv.get("traffic", 0.0) for kv in kernels.values()) or None,
+                "kernel": "whole step (forward + dQ + dK/dV kernels) per GPU; dominant single kernel: "
+                          + (labels[dom] if dom else "n/a"),
+                "dominant_kernel": dom, "kernels": kernels, "peak_kind": f"{peak_kind}, sustained",
                 "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                 "fwd_tflops": F_fwd / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": 2.5 * F_fwd / (bwd_ms * 1e-3) / 1e12,
                 "executed_tflops": executed / (ms * 1e-3) / 1e12 if executed else None,
+                "executed_units_per_step": executed / unit if executed else None,
+                "list_ctas": status.get("list_ctas"), "pass_ctas": status.get("pass_ctas"),
                 "frac_of_burst_peak": value / world / peak, "frac_of_nominal_2250": value / world / 2250.0}
 
     # ---- end to end from pinned host buffers -------------------------------------------------------
@@ -469,9 +502,11 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         Ls = min(L, args.cpu_len)
-        tf, sec, threads = cpu_reference(Ls, D, alpha if alpha is not None else 1.5, causal, 2, 1)
+        tf, sec, threads = cpu_reference(Ls, D, alpha if alpha is not None else 1.5, causal, 3, 1)
         cpu = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "seconds_per_pair": sec,
-               "sample": f"1 of {B * H} (batch, head) pairs at L={Ls} (dense fp32, bisection n_iter=10 + Jacobian backward)"}
+               "sample": f"1 of {B * H} (batch, head) pairs at L={Ls} (dense fp32, bisection n_iter=10 + Jacobian backward), "
+                         "mean of 3 after 1 warm-up",
+               "config1": cpu_config1()}
 
     sparsity = None
     if centres is not None:

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libflashlazy.so")
 FLA_F32, FLA_F16, FLA_BF16 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
 PATH_NAMES = {PATH_AUTO: "auto", PATH_SIMT: "simt", PATH_TCGEN05: "tcgen05"}
-FLAG_NO_CANDIDATE_LIST, FLAG_PLAIN_FIRST_STEP = 1, 2
+FLAG_NO_CANDIDATE_LIST, FLAG_PLAIN_FIRST_STEP, FLAG_CANDIDATE_LIST = 1, 2, 4
 
 
 class Tensor4(C.Structure):
@@ -43,8 +43,7 @@ SIGNATURES = {
     "fla_entmax_bwd": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _f32, C.c_int, _vp]),
     "fla_block_mask_words": (_i64, [_i32]),
     "fla_check_status": (C.c_int, [_vp, _vp]),
-    "fla_entmax_attn_fwd_workspace": (_sz, [_PG]),
-    "fla_entmax_attn_fwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, C.c_int, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "fla_entmax_attn_fwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, C.c_int, _vp, _vp, _vp, _vp, _vp]),
     "fla_entmax_attn_bwd_workspace": (_sz, [_PG]),
     "fla_entmax_attn_bwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, _vp, _vp, _vp, _vp, _P4, _P4, _P4,
                                       _vp, _sz, _vp]),

@@ -47,10 +47,6 @@ struct AttnParams {
   float* dtau;
   // backward scratch
   float* delta;  // [B,H,L]
-  // forward scratch of the tensor-core entmax kernel: per-SM candidate lists (see tc_fwd.cuh)
-  float* list_ws;
-  int list_slots;   // SM slots the workspace holds
-  int list_cap;     // entries per row thread
   int flags;        // FLA_FLAG_* of fla_attn_geom
   int debug;        // development builds (-DFLA_TRACE) only: timing switches; always 0 in the shipped library
 };

@@ -248,6 +248,16 @@ __global__ void __launch_bounds__(256) entmax_bwd_kernel(const void* y, const vo
 // consecutive reductions: a block may already push the next result while a slower one still reads.
 template <int CS>
 struct ClusterSlots { float v[2][CS][3]; };
+// A block may only write into another block's shared memory once that block has started: every block
+// of a cluster arrives at the cluster barrier as its first action and waits for the others just before
+// its first remote store, so that the wait hides behind the row loads.
+__device__ __forceinline__ void cluster_arrive_started() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_started() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 template <int CS>
 __device__ __forceinline__ Sum3 cluster_sum3(Sum3 v, ClusterSlots<CS>* slots, int half, unsigned rank) {
   namespace cg = cooperative_groups;
@@ -330,6 +340,7 @@ __global__ void __launch_bounds__(256, CH * Vec<DT>::NV <= 32 ? 4 : 2) entmax_fw
   static_assert(CS == 1 || GW == 8, "a cluster owns one row, each of its blocks a part of it");
   __shared__ float scratch_all[2 * 8 * 3];   // per row group: two halves of GW*3 floats (see group_sum3_alt)
   __shared__ ClusterSlots<CS> cslots;
+  if (CS > 1) cluster_arrive_started();
   float* scratch = scratch_all + (threadIdx.x >> 5) / GW * (2 * GW * 3);
   constexpr int NV = Vec<DT>::NV, GT = GW * LPR * CS, RW = 32 / LPR, RPB = 8 / GW * RW, N = CH * NV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -359,7 +370,7 @@ __global__ void __launch_bounds__(256, CH * Vec<DT>::NV <= 32 ? 4 : 2) entmax_fw
     }
   }
   m = group_max_g<GW, LPR>(m, scratch, lane, wg, warp - wg);
-  if (CS > 1) m = cluster_max<CS>(m, &cslots, 0, crank);
+  if (CS > 1) { cluster_wait_started(); m = cluster_max<CS>(m, &cslots, 0, crank); }
   if (KIND == 0) m *= am1;
 
   float lo = -1.f, hi = -exp2f(-am1 * log2f((float)cols)), ts = -1.f;
@@ -438,6 +449,7 @@ __global__ void __launch_bounds__(256, Vec<DT>::NV == 8 ? 4 : 3) entmax_bwd_vec_
   static_assert(LPR == 32 || (GW == 1 && CS == 1), "rows that share a warp are owned by that warp alone");
   __shared__ float scratch_all[2 * 8 * 3];
   __shared__ ClusterSlots<CS> cslots;
+  if (CS > 1) cluster_arrive_started();
   float* scratch = scratch_all + (threadIdx.x >> 5) / GW * (2 * GW * 3);
   constexpr int NV = Vec<DT>::NV, GT = GW * LPR * CS, RW = 32 / LPR, RPB = 8 / GW * RW, N = CH * NV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -482,7 +494,7 @@ __global__ void __launch_bounds__(256, Vec<DT>::NV == 8 ? 4 : 3) entmax_bwd_vec_
         }
       }
       s = group_sum3_alt<GW, LPR>(s, scratch, lane, wg, 0, warp - wg);
-      if (CS > 1) s = cluster_sum3<CS>(s, &cslots, 0, crank);
+      if (CS > 1) { cluster_wait_started(); s = cluster_sum3<CS>(s, &cslots, 0, crank); }
       if (!row_ok) return;
       const float q = s.a > 0.f ? s.b / s.a : 0.f;
       // (opaque to the compiler, which would otherwise keep the unpacked values of the first pass alive)
@@ -535,7 +547,7 @@ __global__ void __launch_bounds__(256, Vec<DT>::NV == 8 ? 4 : 3) entmax_bwd_vec_
     else if (kind == 1) weights(std::integral_constant<int, 1>{});
     else weights(std::integral_constant<int, 2>{});
     s = group_sum3_alt<GW, LPR>(s, scratch, lane, wg, 0, warp - wg);
-    if (CS > 1) s = cluster_sum3<CS>(s, &cslots, 0, crank);
+    if (CS > 1) { cluster_wait_started(); s = cluster_sum3<CS>(s, &cslots, 0, crank); }
     if (!row_ok) return;
     const float q = s.a > 0.f ? s.b / s.a : 0.f;
 #pragma unroll

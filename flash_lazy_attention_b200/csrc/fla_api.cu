@@ -222,36 +222,6 @@ int fla_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_
   return e == cudaSuccess ? FLA_OK : cuda_fail(e, "entmax backward launch");
 }
 
-// Candidate lists of the tensor-core forward: entries per row thread and bytes per SM slot.
-static int list_cap_for(int L) {
-  // A row thread sees a quarter of the row.  Short rows: room for all of it; long rows: a sixteenth
-  // of the row (a Gaussian row keeps 7-11 % against the running maximum), at most 2048; plus the 64
-  // entries one tile may add after the last check.
-  const int quarter = (L + 3) / 4, sixteenth = L / 16;
-  int cap = quarter < 512 ? quarter : (sixteenth > 512 ? sixteenth : 512);
-  if (cap > 2048) cap = 2048;
-  return ((cap + 63) & ~63) + 64;
-}
-static size_t list_slot_bytes(int L) { return (size_t)list_cap_for(L) * 512 * sizeof(float); }
-static int sm_count() {
-  constexpr int kMaxDevices = 64;
-  static int counts[kMaxDevices] = {};
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
-  if (counts[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) counts[dev] = n;
-  }
-  return counts[dev];
-}
-
-size_t fla_entmax_attn_fwd_workspace(const fla_attn_geom* g) {
-  if (!g || g->B <= 0 || g->H <= 0 || g->L <= 0 || g->path == FLA_PATH_SIMT) return 0;
-  if (g->dtype != FLA_BF16 && g->dtype != FLA_F16) return 0;
-  if (g->D != 64 && g->D != 128) return 0;
-  return (size_t)sm_count() * list_slot_bytes(g->L);
-}
-
 int fla_check_status(const int32_t* status, void* stream) {
   if (!status) return fail(FLA_ERR_INVALID, "status is NULL");
   int32_t host[4] = {0, 0, 0, 0};
@@ -267,7 +237,7 @@ int fla_check_status(const int32_t* status, void* stream) {
 
 int fla_entmax_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_tensor4* k, const fla_tensor4* v,
                         const fla_tensor4* o, float alpha, int niter, float* tau, float* aux_o, float* aux_s,
-                        uint32_t* block_mask, void* workspace, size_t workspace_bytes, void* stream) {
+                        uint32_t* block_mask, void* stream) {
   FLA_TRY(check_geom(g));
   if (!(alpha > 1.0f && alpha <= 2.0f)) return fail(FLA_ERR_INVALID, "alpha must be in (1, 2], got %g", alpha);
   if (niter < 0) return fail(FLA_ERR_INVALID, "niter must be >= 0");
@@ -282,15 +252,6 @@ int fla_entmax_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_
   p.alpha = alpha; p.niter = niter; p.tau = tau; p.aux_o = aux_o; p.aux_s = aux_s;
   p.block_mask = block_mask;
   p.mask_words = (int)fla_block_mask_words(g->L);
-  if (workspace && ((uintptr_t)workspace & 255) != 0) return fail(FLA_ERR_INVALID, "workspace must be 256-byte aligned");
-  if (workspace) {
-    const size_t slots = workspace_bytes / list_slot_bytes(g->L);
-    if (slots > 0) {
-      p.list_ws = (float*)workspace;
-      p.list_slots = (int)(slots > 4096 ? 4096 : slots);
-      p.list_cap = list_cap_for(g->L);
-    }
-  }
   cudaStream_t st = (cudaStream_t)stream;
   if (block_mask) {
     size_t bytes = (size_t)g->B * g->H * ((g->L + 127) / 128) * p.mask_words * sizeof(uint32_t);

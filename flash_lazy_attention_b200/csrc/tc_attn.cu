@@ -29,16 +29,16 @@ bool view_ok(const View4& v, const char** why) {
   return true;
 }
 
-template <int D>
-constexpr size_t fwd_smem_bytes() {
-  return (size_t)tc::TileCfg<D>::kTileBytes * (1 + tc::TileCfg<D>::kStages) + 1024;
+template <int MODE, int D>
+constexpr size_t fwd_smem_bytes() {   // Q, the K/V ring; entmax: staging slots of the candidate lists
+  return (size_t)tc::TileCfg<D>::kTileBytes * (1 + tc::TileCfg<D>::kStages) + 1024 + (MODE == ENTMAX ? tc::kStageBytes : 0);
 }
 
 template <int MODE, int D, int FMT, int KIND>
 cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        int* status, cudaStream_t st) {
   auto kern = tc::fwd_kernel<MODE, D, FMT, KIND>;
-  constexpr size_t smem = fwd_smem_bytes<D>();
+  constexpr size_t smem = fwd_smem_bytes<MODE, D>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const unsigned grid = (unsigned)(((p.L + 127) / 128) * p.B * p.H);

@@ -153,6 +153,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   const int nkt = tile_live ? (causal ? min((len + 127) >> 7, mt + 1) : ((len + 127) >> 7)) : 0;
   const bool want_dbias = MODE == LAZY && p.dbias != nullptr;
   volatile int* abort_flag = &sh.abort_flag;
+  if (tid == 0) kernel_clock(status, 1, false);
 
   if (tid == 0) {
     mbar_init(&sh.res_full, 1);
@@ -652,6 +653,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   if (*abort_flag) {
     for (int w = 0; w < 2000; ++w) __nanosleep(1000);
   }
+  if (tid == 0) kernel_clock(status, 1, true);
   if (warp == kBwdProducerWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);

@@ -106,6 +106,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__
   const int n_end = (len + 63) >> 6;
   const int nq_all = tile_live ? n_end - n_begin : 0;
   volatile int* abort_flag = &sh.abort_flag;
+  if (tid == 0) kernel_clock(status, 2, false);
 
   if (tid == 0) {
     mbar_init(&sh.res_full, 1);
@@ -390,6 +391,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__
   if (*abort_flag) {
     for (int w = 0; w < 2000; ++w) __nanosleep(1000);
   }
+  if (tid == 0) kernel_clock(status, 2, true);
   if (warp == kKvProducerWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);

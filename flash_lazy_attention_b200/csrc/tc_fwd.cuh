@@ -37,6 +37,12 @@ constexpr int kFwdMmaWarp = 17;
 constexpr int kFwdThreads = 608;
 constexpr uint32_t kProbCol = 384;     // last pass: probability buffers at tensor-memory columns 384 + 64 g
 constexpr int kMaxMaskWords = 64;  // block-mask words per query block: L <= 131072
+// Candidates of the entmax forward: every row thread keeps the scores that can still lie above the row's
+// threshold in kStageSlots private shared-memory slots.
+constexpr int kStageSlots = 24;
+constexpr int kStageKeep = 16;    // most a thread keeps after tightening: 8 slots stay free for the next 8 scores
+constexpr int kPoolSize = 256;    // spill pool of a CTA, (value, row) pairs
+constexpr int kStageBytes = kStageSlots * kFwdRowThreads * 4;
 
 template <int D>
 struct TileCfg {
@@ -73,6 +79,14 @@ struct FwdShared {
   // the other three without synchronisation: a stale value is a smaller one, and any lower bound of
   // the row maximum keeps the candidate filter below a superset filter.
   float rmax[4][128];
+  // The same for the lower bound of the row's threshold each of the four threads derived from its own
+  // candidates ((alpha-1)*score units): any of them, stale or not, is a valid lower bound.
+  float rlb[4][128];
+  // ... and a tangent (value at 0, slope) of each thread's part of f, see the row-max pass.
+  float2 rtan[4][128];
+  // Spill pool: (score, row) pairs of threads that were left with more than kStageKeep candidates.
+  float2 pool[kPoolSize];
+  int npool;
 };
 
 template <int D>
@@ -177,6 +191,78 @@ __device__ __forceinline__ long long trace_clock_dep(float a, float b, float c) 
 #define TRACE(cond, pass_, kt, slot, val) do { } while (0)
 #endif
 
+
+// 8-byte shared-memory accesses that are not cached in registers: other warps write these pairs.
+__device__ __forceinline__ float2 lds_f2(const float2* ptr) {
+  float2 v;
+  asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(smem_u32(ptr)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_f2(float2* ptr, float a, float b) {
+  asm volatile("st.volatile.shared.v2.f32 [%0], {%1, %2};" ::"r"(smem_u32(ptr)), "f"(a), "f"(b) : "memory");
+}
+
+// Streaming candidates of the entmax forward (see the row-max pass of fwd_kernel): Newton steps from the
+// left on "my candidates exactly + the tangents the other three threads of the row published - 1", then
+// publish my tangent and bound, and drop the candidates the bound excludes.  A thread left with more than
+// kStageKeep candidates hands the surplus to the CTA's spill pool (a rare event: the tail of how a row's
+// support splits over its four threads); `kept` = -1 reports that the pool is full.  Not inlined: it is
+// called from two places inside the hottest loop of the kernel and would otherwise take its registers.
+struct TightenResult { float bound; int kept; };
+template <int KIND>
+static __device__ __noinline__ TightenResult tighten_candidates(FwdShared* sh, float* stage_t, int n_st, float t, float c1,
+                                                               float e, int quad, int row, int steps, int keep_if) {
+  // (few registers on purpose: a call that has to save many of its caller's registers goes through local
+  // memory, and with almost all of the SM's memory configured as shared memory that means L2)
+  // the other threads' tangents: sum_j [X_j - t]_+^e >= oc + ob * t over their candidates
+  float oc = 0.f, ob = 0.f;
+#pragma unroll
+  for (int qq = 0; qq < 4; ++qq) {
+    const float2 tg = lds_f2(&sh->rtan[qq][row]);   // (one 8-byte load: a pair is never torn)
+    if (qq != quad) { oc += tg.x; ob += tg.y; }
+  }
+  float te = t, s0 = 0.f, s1 = 0.f;
+#pragma unroll 1
+  for (int it = 0; it < steps; ++it) {
+    te = t; s0 = 0.f; s1 = 0.f;
+#pragma unroll 2
+    for (int j = 0; j < n_st; ++j) {
+      const float d = fmaf(stage_t[j * kFwdRowThreads], c1, -t);   // <= 1: t >= (row maximum so far) - 1
+      if (KIND == 0) { const float ee = __saturatef(d); s0 = fmaf(ee, ee, s0); s1 += ee; }
+      else if (KIND == 1) { s0 += fmaxf(d, 0.f); s1 += d > 0.f ? 1.f : 0.f; }
+      else if (d > 0.f) { float pw, u; p_and_u<2>(d, e, pw, u); s0 += pw; s1 += u; }
+    }
+    const float fv = s0 + fmaf(ob, t, oc) - 1.f;              // <= f(t) of the whole row
+    const float tn = t + __fdividef(fv, fmaf(e, s1, -ob));     // slope -(e s1 - ob) < 0
+    if (!(fv > 0.f) || !(tn > t)) break;
+    t = tn;
+  }
+  // my tangent at the last point evaluated: s0 - e s1 (t - te)
+  sts_f2(&sh->rtan[quad][row], fmaf(e * s1, te, s0), -e * s1);
+  ((volatile float*)&sh->rlb[0][0])[quad * 128 + row] = t;
+  int k = n_st;
+  if (n_st > keep_if) {
+    k = 0;
+#pragma unroll 1
+    for (int j = 0; j < n_st; ++j) {
+      const float v = stage_t[j * kFwdRowThreads];
+      if (fmaf(v, c1, -t) > 0.f) { stage_t[k * kFwdRowThreads] = v; ++k; }
+    }
+    if (k > kStageKeep) {   // hand the surplus to the pool
+      for (int j = kStageKeep; j < k; ++j) {
+        const int pos = atomicAdd(&sh->npool, 1);
+        if (pos < kPoolSize) sh->pool[pos] = make_float2(stage_t[j * kFwdRowThreads], __int_as_float(row));
+        else k = -1 - kStageSlots;   // pool full
+      }
+      k = k < 0 ? -1 : kStageKeep;
+    }
+  }
+  TightenResult r;
+  r.bound = t;
+  r.kept = k;
+  return r;
+}
+
 template <int MODE, int D, int FMT, int KIND>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -186,6 +272,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   uint8_t* smem = align_1024(smem_raw);
   uint8_t* sQ = smem;
   uint8_t* ring = smem + Cfg::kTileBytes;
+  uint8_t* stage = ring + Cfg::kStages * Cfg::kTileBytes;   // entmax only: candidate slots of the row threads
   __shared__ FwdShared sh;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,6 +292,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const bool tile_live = row0 < len;
   const int nkt = tile_live ? (causal ? min((len + 127) >> 7, mt + 1) : ((len + 127) >> 7)) : 0;
   volatile int* abort_flag = &sh.abort_flag;
+  if (tid == 0) kernel_clock(status, 0, false);
 
   if (tid == 0) {
     mbar_init(&sh.q_full, 1);
@@ -226,12 +314,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     fence_mbar_init();
   }
   if (tid < kMaxMaskWords) sh.mask_words[tid] = 0;
-  if (tid < kFwdRowThreads) (&sh.rmax[0][0])[tid] = -INFINITY;
+  if (tid < kFwdRowThreads) {
+    (&sh.rmax[0][0])[tid] = -INFINITY;
+    (&sh.rlb[0][0])[tid] = -INFINITY;
+    (&sh.rtan[0][0])[tid] = make_float2(0.f, 0.f);
+  }
   if (tid < 32) {
     const int lo = tid * 32;
     sh.act[0][tid] = sh.act[1][tid] = nkt >= lo + 32 ? 0xffffffffu : (nkt > lo ? (1u << (nkt - lo)) - 1u : 0u);
     sh.act_next[tid] = 0u;
-    if (tid == 0) sh.force_all = 0;
+    if (tid == 0) { sh.force_all = 0; sh.npool = 0; }
   }
   if (warp == kFwdProducerWarp) tmem_alloc(&sh.tmem_base, 512);
   tc_fence_before_sync();
@@ -461,22 +553,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       if (MODE == ENTMAX) {
         const float c1 = p.scale * (p.alpha - 1.f);
         const float e = 1.f / (p.alpha - 1.f);
-        // Row-max pass.  It also marks the tiles a threshold pass has to visit: tau never
-        // drops below max - 1, so a tile counts only if it holds a score within 1 of the row
-        // maximum; tested against the largest score the four threads of the row have seen so far
-        // (never above the final maximum), which marks a superset.
+        // Row-max pass with streaming candidates.
         //
-        // Candidate list.  Only scores within 1 (in (alpha-1)*score units) of the row maximum can
-        // ever lie above the threshold, a few percent of a long Gaussian row.  While it looks for the
-        // maximum, every row thread appends the scores of its columns that pass that test against
-        // the running maximum to a list of its own in global memory (a superset again: the running
-        // maximum only rises).  The threshold is then iterated on the lists alone: no further
-        // score products, no key tile read again, and the iteration can afford to converge fully.
-        // The lists live in a workspace slot of the SM this CTA runs on (one CTA per SM: each
-        // holds all of its tensor memory); entry x of thread t sits at slot + (x * 512 + t) floats.
-        // A thread whose list would not fit sets the overflow flag; if any does (wide supports:
-        // alpha near 1, tiny scores), or without a workspace, the CTA falls back to threshold
-        // passes over recomputed score tiles.
+        // tau never drops below max - 1, and threads that have seen some of a row's scores can do
+        // better.  With f(t) = sum_j [X_j - t]_+^e - 1 (convex, decreasing; its root is tau): leaving
+        // entries out only lowers f, a tangent of a convex function lies below it, and a Newton step
+        // from the left never passes the root.  So a root of "my candidates exactly + the tangents the
+        // other three threads of the row published for theirs - 1", approached by Newton steps from
+        // the left, is a lower bound of the row's threshold however stale the tangents are.
+        // While it looks for the row maximum, every row thread keeps the scores of its columns that lie
+        // above the best lower bound known for the row in kStageSlots private shared-memory slots; one
+        // candidate costs a predicated shared-memory store and a predicated pointer bump.  After every
+        // 8 scores a warp whose fullest lane has fewer than 8 free slots left tightens: each lane takes
+        // Newton steps as above, publishes its tangent and the new bound, and drops the candidates at
+        // or below it.  On a long Gaussian row the bound closes in on the threshold after a few tiles
+        // and little more than the final support (a fraction of a percent of the row) is ever kept.
+        // At the end of the pass the union of the four threads' candidates contains the row's support,
+        // and the threshold is iterated to convergence on those few values: no further score
+        // products, no key tile read again.  A tile is marked for the last pass iff a candidate was
+        // taken from it.  If some lane cannot get down to kStageSlots - 8 candidates (wide supports:
+        // alpha near 1, tiny scores), the CTA falls back to threshold passes over recomputed score
+        // tiles, which mark tiles by their distance from the running maximum instead.
         float mrow = -INFINITY;
         uint32_t mark_bits = 0;
         int mark_word = 0;
@@ -485,16 +582,32 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (any != 0u && lane == 0) atomicOr(&sh.act_next[mark_word], any);
           mark_bits = 0;
         };
-        uint32_t smid;
-        asm("mov.u32 %0, %%smid;" : "=r"(smid));
-        bool lovf = p.list_ws == nullptr || (int)smid >= p.list_slots || p.niter <= 0 || p.list_cap < 64 ||
-                    (p.flags & FLA_FLAG_NO_CANDIDATE_LIST) != 0;
-        float* const lbase = lovf ? nullptr : p.list_ws + ((size_t)smid * (size_t)p.list_cap) * kFwdRowThreads + tid;
-        float* lw = lbase;
-        // a tile may add up to 64 entries: appending stops once fewer than that are left
-        float* const lstop = lovf ? nullptr : lbase + (size_t)(p.list_cap - 64) * kFwdRowThreads;
-        const float inv_c1 = 1.f / c1;
+        // (uniform over the CTA here, over the warp once a lane has run out of slots)
+        // Which way by default: keeping candidates costs about as much CUDA-core work per score as one
+        // threshold pass (three issue slots per score for the predicated store and pointer bump, plus the
+        // tightening calls).  alpha = 2 pays that once instead of five or six Newton passes; alpha = 1.5,
+        // whose tail-model first step gets by with three passes, comes out slightly behind and keeps the
+        // passes unless the caller asks for candidates.
+        bool lovf = p.niter <= 0 || (p.flags & FLA_FLAG_NO_CANDIDATE_LIST) != 0 ||
+                    (KIND != 1 && (p.flags & FLA_FLAG_CANDIDATE_LIST) == 0);
+        float* const stage_t = reinterpret_cast<float*>(stage) + tid;  // slot x of this thread: stage_t[x * 512]
+        const uint32_t sa0 = smem_u32(stage_t);
+        uint32_t sa = sa0;
+        float tlb = -INFINITY;   // this thread's lower bound of the row threshold, (alpha-1)*score units
+        uint32_t ntile = 0;      // tiles this thread has worked on
+        volatile float* rlb = &sh.rlb[0][0];
         volatile float* rmx = &sh.rmax[0][0];
+        // steps: Newton steps to take; keep_if: compact only if more than this many candidates are held
+        auto tighten = [&](int steps, int keep_if) {
+          const float blb = fmaxf(fmaxf(rlb[row], rlb[128 + row]), fmaxf(rlb[256 + row], rlb[384 + row]));
+          const float msh_x = fmaxf(fmaxf(rmx[row], rmx[128 + row]), fmaxf(rmx[256 + row], rmx[384 + row])) * c1;
+          const TightenResult tr = tighten_candidates<KIND>(&sh, stage_t, (int)((sa - sa0) >> 11), fmaxf(msh_x - 1.f, blb),
+                                                            c1, e, quad, row, steps, keep_if);
+          tlb = tr.bound;
+          sa = sa0 + (uint32_t)max(tr.kept, 0) * 2048u;
+          if (__any_sync(0xffffffffu, tr.kept < 0)) lovf = true;   // the spill pool is full
+        };
+        const float inv_c1 = 1.f / c1;
         for_my_tiles(0, [&](int kt, uint32_t cs) {
           const uint32_t buf = cs & 3;
           if ((kt >> 5) != mark_word) { publish_marks(); mark_word = kt >> 5; }
@@ -526,31 +639,59 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           rmx[quad * 128 + row] = mrow;
           const float msh = fmaxf(fmaxf(rmx[row], rmx[128 + row]), fmaxf(rmx[256 + row], rmx[384 + row]));
           const bool near_max = tm > -INFINITY && (msh - tm) * c1 < 1.f;
-          mark_bits |= (near_max ? 1u : 0u) << (kt & 31);
-          if (!lovf) {
-            if (lw > lstop) {
-              lovf = true;
-            } else {
-              // masked entries are -inf and never pass; one predicated store and pointer bump each
-              const float thr = msh - inv_c1;
+          bool took = false;
+          if (!lovf && !FLA_DBG(p, 2048)) {
+            // raw-score form of the row's best lower bound; masked entries are -inf and never pass
+            const float blb = fmaxf(fmaxf(rlb[row], rlb[128 + row]), fmaxf(rlb[256 + row], rlb[384 + row]));
+            const float thr = fmaxf(msh - inv_c1, blb * inv_c1);
 #pragma unroll
-              for (int x = 0; x < 64; ++x)
+            for (int x0 = 0; x0 < 64; x0 += 8) {
+              if (lovf) break;   // (a lane ran out of slots: nothing more is staged)
+              const uint32_t sa_in = sa;
+#pragma unroll
+              for (int x = x0; x < x0 + 8; ++x)
                 asm volatile(
                     "{\n\t.reg .pred p;\n\t"
                     "setp.gt.f32 p, %1, %2;\n\t"
-                    "@p st.global.f32 [%0], %1;\n\t"
-                    "@p add.u64 %0, %0, 2048;\n\t}"
-                    : "+l"(lw)
+                    "@p st.shared.f32 [%0], %1;\n\t"
+                    "@p add.u32 %0, %0, 2048;\n\t}"
+                    : "+r"(sa)
                     : "f"(__uint_as_float(r[x])), "f"(thr)
                     : "memory");
+              took |= sa != sa_in;
+              if (__any_sync(0xffffffffu, sa - sa0 > (uint32_t)(kStageSlots - 8) * 2048u)) {
+#ifdef FLA_TRACE
+                if (lane == 0 && status) atomicAdd(status + 20, 1);
+#endif
+                if (FLA_DBG(p, 512)) sa = sa0; else
+                tighten(3, 0);
+              }
             }
           }
+          // One Newton step at the end of a tile keeps the published tangents fresh and the bound close to
+          // the threshold of what the row has shown so far; the bound moves less and less, so the steps
+          // thin out: after the thread's tiles 1-4, then 6, 8, 12, 16, 24, 32, ...
+          ++ntile;
+          {
+            const uint32_t third = ntile / 3u;
+            const bool due = ntile <= 4u || (ntile & (ntile - 1u)) == 0u || (third * 3u == ntile && (third & (third - 1u)) == 0u);
+            if (!lovf && due) {
+#ifdef FLA_TRACE
+              if (lane == 0 && status) atomicAdd(status + 21, 1);
+#endif
+              if (!FLA_DBG(p, 1024))
+              tighten(1, 8);
+            }
+          }
+          mark_bits |= ((lovf ? near_max : took) ? 1u : 0u) << (kt & 31);
           TRACE((tid & 127) == 0 && half == 0, 1, kt, 7, trace_clock());
         });
         publish_marks();
         sh.part[quad][0][row] = mrow;
+        sh.part[quad][1][row] = tlb;
         named_bar_sync(1, kFwdRowThreads);
         float m = fmaxf(fmaxf(sh.part[0][0][row], sh.part[1][0][row]), fmaxf(sh.part[2][0][row], sh.part[3][0][row]));
+        const float row_lb = fmaxf(fmaxf(sh.part[0][1][row], sh.part[1][1][row]), fmaxf(sh.part[2][1][row], sh.part[3][1][row]));
         if (warp == 0) {
           // tiles of the next pass (all of them if nothing was marked: non-finite scores)
           const int lo_t = lane * 32;
@@ -585,47 +726,63 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           return false;
         };
         if (use_list) {
-          // ---- threshold iteration on the candidate lists: the producer and the issuers go straight
-          // to the last pass (tiles marked by the row-max pass) while the row threads iterate
+          // ---- threshold iteration on the candidates: the producer and the issuers go straight to the
+          // last pass (tiles a candidate was taken from) while the row threads iterate
           signal_pass(false);
           rpass = 1;
-          const int lcnt = (int)((lw - lbase) / kFwdRowThreads);
           if (tid == 0 && status) atomicAdd(status + 6, 1);
+          const int n_st = (int)((sa - sa0) >> 11);
+          const int npool = min(*(volatile int*)&sh.npool, kPoolSize);
+#ifdef FLA_TRACE
+          if (status) { atomicAdd(status + 23, n_st); if (tid == 0) atomicAdd(status + 22, npool); }
+#endif
+          // start from the row's best lower bound (still left of the root)
+          if (live && row_lb - m > ts) { ts = fminf(row_lb - m, hi); lo = ts; }
           for (int it = 0; it < p.niter; ++it) {
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f;
             const float noff = -(m + ts);   // d = X - tau with X = s*c1
-            auto acc = [&](float sv, float& s0, float& s1, float& s2) {
-              const float d = fmaf(sv, c1, noff);
+            for (int j = 0; j < n_st; ++j) {
+              const float d = fmaf(stage_t[j * kFwdRowThreads], c1, noff);
               if (KIND == 0) {
                 const float ee = __saturatef(d);   // d <= 1 on the whole bracket
-                s0 = fmaf(ee, ee, s0); s1 += ee; s2 += d > 0.f ? 1.f : 0.f;
+                a0 = fmaf(ee, ee, a0); a1 += ee; a2 += d > 0.f ? 1.f : 0.f;
               } else if (KIND == 1) {
-                s0 += fmaxf(d, 0.f); s1 += d > 0.f ? 1.f : 0.f;
+                a0 += fmaxf(d, 0.f); a1 += d > 0.f ? 1.f : 0.f;
               } else if (d > 0.f) {
                 float pw, u;
                 p_and_u<2>(d, e, pw, u);
-                s0 += pw; s1 += u; s2 += __fdividef(u, d);
+                a0 += pw; a1 += u; a2 += __fdividef(u, d);
               }
-            };
-            int x = 0;
-            for (; x + 8 <= lcnt; x += 8) {   // eight loads in flight per thread: the lists sit in L2
-              float vv[8];
-#pragma unroll
-              for (int y = 0; y < 8; ++y) vv[y] = __ldcg(lbase + (size_t)(x + y) * kFwdRowThreads);
-#pragma unroll
-              for (int y = 0; y < 8; y += 2) { acc(vv[y], a0, a1, a2); acc(vv[y + 1], b0, b1, b2); }
             }
-            for (; x < lcnt; ++x) acc(__ldcg(lbase + (size_t)x * kFwdRowThreads), a0, a1, a2);
-            sh.part[quad][0][row] = a0 + b0;
-            sh.part[quad][1][row] = a1 + b1;
-            sh.part[quad][2][row] = a2 + b2;
+            // spilled candidates: pool entry i is summed by thread i mod 4 of its row
+            for (int i2 = quad; i2 < npool; i2 += 4) {
+              const float2 pe = sh.pool[i2];
+              if (__float_as_int(pe.y) == row) {
+                const float d = fmaf(pe.x, c1, noff);
+                if (KIND == 0) {
+                  const float ee = __saturatef(d);
+                  a0 = fmaf(ee, ee, a0); a1 += ee; a2 += d > 0.f ? 1.f : 0.f;
+                } else if (KIND == 1) {
+                  a0 += fmaxf(d, 0.f); a1 += d > 0.f ? 1.f : 0.f;
+                } else if (d > 0.f) {
+                  float pw, u;
+                  p_and_u<2>(d, e, pw, u);
+                  a0 += pw; a1 += u; a2 += __fdividef(u, d);
+                }
+              }
+            }
+            sh.part[quad][0][row] = a0;
+            sh.part[quad][1][row] = a1;
+            sh.part[quad][2][row] = a2;
             named_bar_sync(1, kFwdRowThreads);
             if (!done) {
               const float sum0 = (sh.part[0][0][row] + sh.part[1][0][row]) + (sh.part[2][0][row] + sh.part[3][0][row]);
               const float sum1 = (sh.part[0][1][row] + sh.part[1][1][row]) + (sh.part[2][1][row] + sh.part[3][1][row]);
               const float sum2v = (sh.part[0][2][row] + sh.part[1][2][row]) + (sh.part[2][2][row] + sh.part[3][2][row]);
-              // an iteration costs a few thousand cycles here, not a pass over the keys: converge
-              update_tau(sum0, sum1, sum2v, it, kListTolHalley, kListTolNewton, kListTol);
+              // an iteration costs a few hundred cycles here, not a pass over the keys: converge.  (No
+              // tail-model first step: the candidates below the lower bound are gone, and with them the
+              // moments at max - 1 that step is fitted to.)
+              update_tau(sum0, sum1, sum2v, it + 1, kListTolHalley, kListTolNewton, kListTol);
             }
             // (the barrier also orders this iteration's reads of the partial sums before the next writes)
             if (named_bar_and(2, kFwdRowThreads, done || *abort_flag != 0)) break;
@@ -987,6 +1144,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   if (*abort_flag) {  // leave time for copies still in flight before the shared memory is released
     for (int w = 0; w < 2000; ++w) __nanosleep(1000);
   }
+  if (tid == 0) kernel_clock(status, 0, true);
   if (warp == kFwdProducerWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);

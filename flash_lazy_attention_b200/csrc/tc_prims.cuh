@@ -101,6 +101,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return mbar_wait_slow(bar, parity, abort_flag, status, tag, limit);
 }
 
+// Kernel clocks for the caller's status words (fla_attn_geom.status, int32[32], 8-byte aligned): kernel
+// `which` (0 forward, 1 dQ, 2 dK/dV) keeps the earliest start and the latest end of its CTAs, in
+// nanoseconds of the GPU's global timer, at 64-bit words 4 + 2 which (bitwise complement of the start,
+// so that the zero the caller clears the words to means "not set") and 5 + 2 which.
+__device__ __forceinline__ void kernel_clock(int* status, int which, bool end) {
+  if (status == nullptr) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  unsigned long long* w = reinterpret_cast<unsigned long long*>(status + 8) + 2 * which;
+  if (end) atomicMax(w + 1, t); else atomicMax(w, ~t);
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -77,17 +77,18 @@ _status_bufs: dict = {}
 
 
 def _status_buf(device: torch.device) -> torch.Tensor:
-    """Per-device int32[8] the tensor-core kernels report into (see fla_attn_geom.status)."""
+    """Per-device int32[32] the tensor-core kernels report into (see fla_attn_geom.status)."""
     key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
     buf = _status_bufs.get(key)
     if buf is None:
-        buf = torch.zeros(8, dtype=torch.int32, device=device)
+        buf = torch.zeros(32, dtype=torch.int32, device=device)
         _status_bufs[key] = buf
     return buf
 
 
 def read_status(device=None, reset: bool = False) -> dict:
-    """Synchronising read of the device status words: {"error", "wait_tag", "block", "tile_mmas"}.
+    """Synchronising read of the device status words: {"error", "wait_tag", "block", "tile_mmas",
+    "list_ctas", "pass_ctas", "kernel_ms"}.
     ``tile_mmas`` counts 128x128xD tile products issued by tensor-core kernels since the last reset."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     buf = _status_buf(device)
@@ -96,7 +97,17 @@ def read_status(device=None, reset: bool = False) -> dict:
         buf.zero_()
     return {"error": vals[0], "wait_tag": vals[1], "block": vals[2],
             "tile_mmas": (vals[4] & 0xFFFFFFFF) | ((vals[5] & 0xFFFFFFFF) << 32),
-            "list_ctas": vals[6], "pass_ctas": vals[7]}
+            "list_ctas": vals[6], "pass_ctas": vals[7], "kernel_ms": _kernel_ms(vals)}
+
+
+def _kernel_ms(vals) -> dict:
+    """Durations the kernels clocked themselves (earliest CTA start to latest CTA end, GPU global timer)
+    since the status words were last cleared; None for a kernel that did not run."""
+    out = {}
+    for i, name in enumerate(("fwd", "dq", "dkdv")):
+        w = [(vals[8 + 4 * i + 2 * j] & 0xFFFFFFFF) | ((vals[9 + 4 * i + 2 * j] & 0xFFFFFFFF) << 32) for j in range(2)]
+        out[name] = None if w[0] == 0 or w[1] == 0 else (w[1] - ((~w[0]) & 0xFFFFFFFFFFFFFFFF)) * 1e-6
+    return out
 
 
 def check_status(device=None) -> None:
@@ -121,11 +132,6 @@ def _geom(q: torch.Tensor, causal: bool, varlen32) -> AttnGeom:
     g.flags = _flags
     return g
 
-
-def _fwd_workspace(lib, g, device):
-    """Scratch of the tensor-core forward (candidate lists); None when it has no use for any."""
-    nbytes = lib.fla_entmax_attn_fwd_workspace(g)
-    return torch.empty((nbytes,), dtype=torch.uint8, device=device) if nbytes else None
 
 
 def _varlen32(varlen, q):
@@ -172,13 +178,10 @@ class EntmaxAttnFunc(torch.autograd.Function):
             if use_block_mask:
                 words = lib.fla_block_mask_words(L)
                 mask = torch.empty((B, H, (L + 127) // 128, words), dtype=torch.int32, device=q.device)
-            ws = _fwd_workspace(lib, g, q.device)
             rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), float(alpha), int(niter),
                                          tau.data_ptr(), aux_o.data_ptr() if need_aux else None,
                                          aux_s.data_ptr() if need_aux else None,
-                                         mask.data_ptr() if mask is not None else None,
-                                         ws.data_ptr() if ws is not None else None,
-                                         ws.numel() if ws is not None else 0, _stream(q))
+                                         mask.data_ptr() if mask is not None else None, _stream(q))
             _lib.check(rc, "fla_entmax_attn_fwd")
         ctx.save_for_backward(q, k, v, tau, aux_o, aux_s, mask, vl)
         ctx.alpha, ctx.is_causal = float(alpha), bool(is_causal)
@@ -233,13 +236,10 @@ def entmax_attention_forward(q, k, v, alpha=1.5, niter=10, is_causal=False, varl
             mask = torch.empty((B, H, (L + 127) // 128, lib.fla_block_mask_words(L)), dtype=torch.int32,
                                device=q.device)
         g = _geom(q, is_causal, vl)
-        ws = _fwd_workspace(lib, g, q.device)
         rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), float(alpha),
                                      int(niter), tau.data_ptr(), aux_o.data_ptr() if need_aux else None,
                                      aux_s.data_ptr() if need_aux else None,
-                                     mask.data_ptr() if mask is not None else None,
-                                     ws.data_ptr() if ws is not None else None,
-                                     ws.numel() if ws is not None else 0, _stream(q))
+                                     mask.data_ptr() if mask is not None else None, _stream(q))
         _lib.check(rc, "fla_entmax_attn_fwd")
     return out, tau, aux_o, aux_s, mask
 

@@ -44,13 +44,15 @@ extern "C" {
 #define FLA_PATH_SIMT 1     /* fp32 CUDA-core kernels: any dtype, any D <= 128               */
 #define FLA_PATH_TCGEN05 2  /* tcgen05 + TMEM + TMA kernels: bf16/fp16, D in {64,128}        */
 
-/* fla_attn_geom.flags (a sum of bits; 0 in normal use).  Both change how the tensor-core
+/* fla_attn_geom.flags (a sum of bits; 0 in normal use).  They change how the tensor-core
  * forward of entmax attention finds the row thresholds, not what it computes; tests use them to
  * reach every code path.                                                                       */
 #define FLA_FLAG_NO_CANDIDATE_LIST 1  /* iterate the thresholds by passes over recomputed score  *
-                                       * tiles even when a candidate-list workspace is given     */
+                                       * tiles instead of on the candidates kept by the first pass */
 #define FLA_FLAG_PLAIN_FIRST_STEP 2   /* alpha = 1.5: plain Halley first step instead of the      *
                                        * tail-model step                                         */
+#define FLA_FLAG_CANDIDATE_LIST 4     /* iterate the thresholds on kept candidates for every      *
+                                       * alpha (the default does so for alpha = 2 only)          */
 
 /* A strided [B,H,L,D] view; strides in elements, stride[3] must be 1. */
 typedef struct fla_tensor4 {
@@ -65,13 +67,17 @@ typedef struct fla_attn_geom {
   int32_t causal;         /* entmax attention only; Lazy Attention is always causal           */
   const int32_t* varlen;  /* device int32 [B]: valid leading tokens per sequence, or NULL      */
   int32_t path;           /* FLA_PATH_*                                                        */
-  int32_t* status;        /* device int32[8] or NULL.  Tensor-core kernels report here:        *
+  int32_t* status;        /* device int32[32], 8-byte aligned, or NULL.  Tensor-core kernels     *
+                           * report here:                                                         *
                            * [0] != 0: a bounded wait ran out ([1] which wait, [2] which block); *
                            * [4],[5]: low/high word of a running count of 128x128xD tile         *
                            * products issued (the "executed FLOPs" figure); [6],[7]: forward     *
-                           * CTAs that iterated the thresholds on candidate lists / by passes     *
-                           * over score tiles.  Never cleared by the library; the caller zeroes   *
-                           * it.                                                                  */
+                           * CTAs that iterated the thresholds on kept candidates / by passes    *
+                           * over score tiles; [8..19]: as 64-bit words, per kernel (forward, dQ,  *
+                           * dK/dV) the bitwise complement of the earliest start and the latest   *
+                           * end of its CTAs in nanoseconds of the GPU's global timer (0 = not    *
+                           * set): the live per-kernel durations of the benchmark.  Never cleared  *
+                           * by the library; the caller zeroes it.                                */
   int32_t flags;          /* FLA_FLAG_*                                                         */
 } fla_attn_geom;
 
@@ -85,7 +91,7 @@ const char* fla_last_error(void);
 int fla_device_supported(int device);
 
 /* Waits for `stream` and reads the status words a tensor-core kernel reports into
- * (fla_attn_geom.status, device int32[8]).  Returns FLA_ERR_DEVICE, with the wait and the block
+ * (fla_attn_geom.status, device int32[32]).  Returns FLA_ERR_DEVICE, with the wait and the block
  * in fla_last_error(), if a bounded wait of a kernel ran out since the words were last cleared:
  * the results of that launch are not valid.  FLA_OK otherwise.  The only entry point that
  * synchronises; callers that never call it pay nothing.                                       */
@@ -128,15 +134,8 @@ int64_t fla_block_mask_words(int32_t L);
 int fla_entmax_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_tensor4* k,
                         const fla_tensor4* v, const fla_tensor4* o, float alpha, int niter,
                         float* tau, float* aux_o, float* aux_s, uint32_t* block_mask,
-                        void* workspace, size_t workspace_bytes, void* stream);
+                        void* stream);
 
-/* Bytes of scratch the forward can use for this geometry on the current device (0 when it has
- * no use for any).  workspace (256-byte aligned) may be NULL or smaller: the tensor-core forward
- * then finds the thresholds by repeated passes over recomputed score tiles, which is slower, with
- * the same results.  With the workspace every row thread keeps the few percent of its scores that
- * can lie above the threshold in a list (one slot of lists per SM) and iterates on those; contents
- * are scratch, nothing needs clearing, and two forwards that overlap on the GPU must not share it. */
-size_t fla_entmax_attn_fwd_workspace(const fla_attn_geom* g);
 
 /* Bytes of caller-provided scratch the backward needs for this geometry. */
 size_t fla_entmax_attn_bwd_workspace(const fla_attn_geom* g);

@@ -28,6 +28,7 @@ from .entmax_ref import (  # noqa: F401
     block_mask_ref,
     bisect10_entmax,
     cpu_reference_fwd_bwd,
+    entmax_attention_rows_ref,
 )
 from .lazy_ref import (lazy_attention_ref, lazy_attention_grads_ref,  # noqa: F401
-                       lazy_attention_grads_analytic)
+                       lazy_attention_grads_analytic, lazy_attention_rows_ref)

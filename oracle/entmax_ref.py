@@ -220,3 +220,42 @@ def cpu_reference_fwd_bwd(q, k, v, do, alpha=1.5, is_causal=True, n_iter=10):
     dq = torch.matmul(ds, k)
     dk = torch.matmul(ds.transpose(-1, -2), q)
     return out, dq, dk, dv, time.perf_counter() - t0
+
+
+def entmax_attention_rows_ref(q, k, v, do, rows, alpha=1.5, is_causal=False, length=None,
+                              work_dtype=torch.float32, round_to=None):
+    """The same mathematics as ``entmax_attention_bwd_ref`` for ONE (batch, head) pair and a subset
+    of its query rows, so that long sequences can be checked with bounded memory.
+
+    ``q, k, v, do``: [L, D]; ``rows``: 1-D int64 tensor of query rows; ``length``: valid leading
+    tokens (``varlen`` of this batch element).  Returns a dict with ``out``, ``dq`` [R, D],
+    ``tau`` [R] and the dense row blocks ``p``, ``ds`` [R, L] (rounded to ``round_to`` when given,
+    as the second products see them).  dK and dV of a key range are
+    ``ds[:, keys].T @ q[rows] / sqrt(D)`` and ``p[:, keys].T @ do[rows]`` once ``rows`` holds every
+    row that can see those keys.  Rows at or beyond ``length`` give zeros."""
+    L, D = q.shape
+    n = L if length is None else int(length)
+    kf, vf = k.to(work_dtype), v.to(work_dtype)
+    qr, dor = q[rows].to(work_dtype), do[rows].to(work_dtype)
+    s = qr @ kf.t() / math.sqrt(D)
+    cols = torch.arange(L)
+    valid = (cols[None, :] < n).expand(len(rows), L).clone()
+    if is_causal:
+        valid &= cols[None, :] <= rows[:, None]
+    live = (rows < n)[:, None]
+    X = s.masked_fill(~valid, -torch.inf) * (alpha - 1.0)
+    tau = _tau_bisect(X, alpha, 64)
+    p = (X - tau).clamp(min=0).pow(1.0 / (alpha - 1.0))
+    p = torch.where(valid & live, p, torch.zeros_like(p))
+    dor = dor * live.to(work_dtype)
+
+    def rnd(t):
+        return t if round_to is None else t.to(round_to).to(work_dtype)
+
+    out = p.to(q.dtype).to(work_dtype) @ vf
+    dp = dor @ vf.t()
+    ds = entmax_bwd_ref(p, dp, alpha)
+    ds = rnd(torch.where(p > 0, ds, torch.zeros_like(ds)))
+    dq = ds @ kf / math.sqrt(D)
+    return {"out": out, "dq": dq, "tau": torch.where(live[:, 0], tau[:, 0], torch.zeros_like(tau[:, 0])),
+            "p": rnd(p), "ds": ds}

@@ -121,3 +121,49 @@ def lazy_attention_grads_analytic(q, k, v, bias, tau, do, window_size=None, varl
         dbias[:, w] = torch.diagonal(ds_h, offset=-w, dim1=-2, dim2=-1).sum(-1)
     dtau = (mda.sum(-1) / (idx + 1).to(work_dtype)).sum(dim=(0, 2)).view(tau.shape)
     return out, dq, dk, dv, dbias, dtau
+
+
+def lazy_attention_rows_ref(q, k, v, do, bias_h, tau_h, rows, window_size, length=None,
+                            work_dtype=torch.float32, round_to=None):
+    """``lazy_attention_grads_analytic`` for ONE (batch, head) pair and a subset of its query rows
+    (bounded memory at long sequences).  ``q, k, v, do``: [L, D]; ``bias_h``: [W'] row of the bias
+    table of this head; ``tau_h``: scalar; ``rows``: 1-D int64 tensor.  Returns a dict with
+    ``out``, ``dq`` [R, D], the dense row blocks ``a`` (rounded to ``round_to``) and ``ds``
+    (``ds`` unrounded for dbias, ``ds_r`` rounded for the products) [R, L], and this block's
+    contributions ``dbias`` [W'] and ``dtau`` (scalar).  dK / dV of a key range follow from
+    ``ds_r[:, keys].T @ q[rows] / sqrt(D)`` and ``a[:, keys].T @ do[rows]`` once ``rows`` holds
+    every row that can see those keys."""
+    L, D = q.shape
+    n = L if length is None else int(length)
+    W = int(window_size)
+    kf, vf = k.to(work_dtype), v.to(work_dtype)
+    qr, dor = q[rows].to(work_dtype), do[rows].to(work_dtype)
+    bf = bias_h.to(work_dtype)
+    scale = 1.0 / math.sqrt(D)
+    cols = torch.arange(L)
+    dist = rows[:, None] - cols[None, :]
+    in_win = (dist >= 0) & (dist < W)
+    s = qr @ kf.t() * scale
+    s = s + bf[dist.clamp(0, max(W - 1, 0)).clamp(max=bf.shape[0] - 1)] * in_win.to(work_dtype)
+    valid = (dist >= 0) & (cols[None, :] < n)
+    live = (rows < n)[:, None]
+    p = torch.softmax(s.masked_fill(~valid, -torch.inf), dim=-1)
+    p = torch.where(valid, p, torch.zeros_like(p))
+    tau_term = tau_h.to(work_dtype) / (rows + 1).to(work_dtype)[:, None]
+    m = ((p + tau_term) > 0) & valid & live
+    a = torch.where(m, p + tau_term, torch.zeros_like(p))
+
+    def rnd(t):
+        return t if round_to is None else t.to(round_to).to(work_dtype)
+
+    dor = dor * live.to(work_dtype)
+    out = rnd(a) @ vf
+    da = dor @ vf.t()
+    mda = torch.where(m, da, torch.zeros_like(da))
+    delta = (p * mda).sum(-1, keepdim=True)
+    ds = p * (mda - delta) * (valid & live).to(work_dtype)
+    dq = rnd(ds) @ kf * scale
+    dbias = torch.zeros_like(bf)
+    dbias.index_add_(0, dist.clamp(0, bf.shape[0] - 1).reshape(-1), (ds * in_win.to(work_dtype)).reshape(-1))
+    dtau = (mda.sum(-1) / (rows + 1).to(work_dtype)).sum()
+    return {"out": out, "dq": dq, "a": rnd(a), "ds": ds, "ds_r": rnd(ds), "dbias": dbias, "dtau": dtau}

@@ -50,16 +50,15 @@ def test_invalid_arguments_are_rejected_without_a_gpu():
     t = _lib.Tensor4()
     t.ptr = p.value
     t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 16 * 256, 16 * 256, 256, 1
-    assert lib.fla_entmax_attn_fwd(g, t, t, t, t, 1.5, 10, p, None, None, None, None, 0, None) == 2  # D > 128
+    assert lib.fla_entmax_attn_fwd(g, t, t, t, t, 1.5, 10, p, None, None, None, None) == 2  # D > 128
     g.D = 16
-    assert lib.fla_entmax_attn_fwd(g, t, t, t, t, 1.5, 10, None, None, None, None, None, 0, None) == 1  # tau NULL
+    assert lib.fla_entmax_attn_fwd(g, t, t, t, t, 1.5, 10, None, None, None, None, None) == 1  # tau NULL
     t2 = _lib.Tensor4()
     t2.ptr = p.value
     t2.stride[0], t2.stride[1], t2.stride[2], t2.stride[3] = 256, 256, 1, 16
-    assert lib.fla_entmax_attn_fwd(g, t2, t, t, t, 1.5, 10, p, None, None, None, None, 0, None) == 1  # inner stride
+    assert lib.fla_entmax_attn_fwd(g, t2, t, t, t, 1.5, 10, p, None, None, None, None) == 1  # inner stride
     assert b"stride" in lib.fla_last_error()
     assert lib.fla_entmax_attn_bwd_workspace(g) == 256
-    assert lib.fla_entmax_attn_fwd_workspace(g) == 0     # fp32, D = 16: no tensor-core forward, no scratch
     assert lib.fla_check_status(None, None) == 1
     assert lib.fla_entmax_attn_bwd(g, t, t, t, t, 1.5, p, p, p, None, t, t, t, p, 8, None) == 1  # workspace
     assert lib.fla_lazy_attn_fwd(g, t, t, t, t, p, 4, p, 8, p, None, None) == 1  # window > bias columns

@@ -179,9 +179,10 @@ def test_block_skipping_backward_matches_oracle_and_unmasked_variant(causal, alp
         results[name] = [out] + [t.grad for t in leaves]
         for nm, mine, r in zip(("out", "dq", "dk", "dv"), results[name], ref):
             assert close(mine, r, dtype), (name, nm, maxdiff(mine, r))
-    # skipping empty blocks must not change anything beyond the ties at the threshold
+    # skipping empty blocks must not change anything beyond the ties at the threshold (and the last place of
+    # a 16-bit value where sums are formed over different tile sets)
     for a, b in zip(results["block_mask"], results["no_block_mask"]):
-        assert maxdiff(a, b) <= 2e-2
+        assert close(a, b, dtype), maxdiff(a, b)
     _, _, _, _, mask = entmax_attention_forward(q, k, v, alpha, 10, causal, None, use_block_mask=True)
     density = unpack_block_mask(mask, L).float().mean().item()
     assert density < 0.6, density        # the input really is block sparse
@@ -190,7 +191,7 @@ def test_block_skipping_backward_matches_oracle_and_unmasked_variant(causal, alp
 @pytest.mark.gpu
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("dist", ["gauss", "heavy"])
-def test_thresholds_of_long_rows_are_tight(causal, dist, monkeypatch):
+def test_thresholds_of_long_rows_are_tight(causal, dist):
     """Rows with hundreds of entries above max-1 take the tail-model first step (alpha = 1.5) and stop
     after a short regular step; the thresholds must still agree with the converged oracle far inside
     the 16-bit tolerance, with and without that first step."""
@@ -204,11 +205,15 @@ def test_thresholds_of_long_rows_are_tight(causal, dist, monkeypatch):
     v = randn((B, H, L, D), dtype, 3)
     _, tau_ref = entmax_attention_probs_ref(q.cpu(), k.cpu(), 1.5, varlen=None, is_causal=causal)
     results = []
-    for debug in ("0", "128"):            # 128: the plain Halley first step
-        monkeypatch.setenv("FLA_DEBUG", debug)
-        out, tau, _, _, _ = entmax_attention_forward(q, k, v, 1.5, 10, causal, None, use_block_mask=True)
+    from flash_lazy_attention_b200 import _lib, set_flags
+    for flags in (0, _lib.FLAG_PLAIN_FIRST_STEP, _lib.FLAG_CANDIDATE_LIST):   # tail-model step / plain Halley / candidates
+        set_flags(flags)
+        try:
+            out, tau, _, _, _ = entmax_attention_forward(q, k, v, 1.5, 10, causal, None, use_block_mask=True)
+        finally:
+            set_flags(0)
         assert last_call_info()["path"] == "tcgen05"
-        assert maxdiff(tau, tau_ref) <= 5e-4, (debug, maxdiff(tau, tau_ref))
+        assert maxdiff(tau, tau_ref) <= 5e-4, (flags, maxdiff(tau, tau_ref))
         results.append((out.float(), tau))
     assert maxdiff(results[0][1], results[1][1]) <= 2e-4
     assert maxdiff(results[0][0], results[1][0]) <= 2e-2

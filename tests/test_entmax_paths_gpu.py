@@ -1,5 +1,5 @@
-"""The two ways the tensor-core forward finds the row thresholds (candidate lists / passes over
-recomputed score tiles) against each other and the oracle, padding that holds NaN, and the
+"""The two ways the tensor-core forward finds the row thresholds (candidates kept by the first pass /
+passes over recomputed score tiles) against each other and the oracle, padding that holds NaN, and the
 status check of the C ABI."""
 import pytest
 import torch
@@ -34,7 +34,7 @@ def test_candidate_lists_and_score_passes_agree(alpha, causal, L, D):
     q, k, v = (randn((B, H, L, D), dtype, s) for s in (1, 2, 3))
     _, tau_ref = entmax_attention_probs_ref(q.cpu(), k.cpu(), alpha, varlen=None, is_causal=causal)
     res = {}
-    for name, flags in (("lists", 0), ("passes", _lib.FLAG_NO_CANDIDATE_LIST)):
+    for name, flags in (("lists", _lib.FLAG_CANDIDATE_LIST), ("passes", _lib.FLAG_NO_CANDIDATE_LIST)):
         set_flags(flags)
         read_status(q.device, reset=True)
         out, tau, _, _, mask = entmax_attention_forward(q, k, v, alpha, 10, causal, None, use_block_mask=True)
@@ -44,7 +44,7 @@ def test_candidate_lists_and_score_passes_agree(alpha, causal, L, D):
     tiles = B * H * ((L + 127) // 128)
     assert res["passes"][3]["pass_ctas"] == tiles and res["passes"][3]["list_ctas"] == 0
     assert res["lists"][3]["list_ctas"] + res["lists"][3]["pass_ctas"] == tiles
-    if alpha >= 1.5:      # few candidates: every CTA's lists fit
+    if alpha >= 1.5:      # small supports: the candidates fit the slots and the spill pool
         assert res["lists"][3]["list_ctas"] == tiles, res["lists"][3]
         # no score product beyond row max + S + P.V
         assert res["lists"][3]["tile_mmas"] < res["passes"][3]["tile_mmas"]
@@ -54,11 +54,12 @@ def test_candidate_lists_and_score_passes_agree(alpha, causal, L, D):
 
 
 def test_list_overflow_falls_back_to_score_passes():
-    """Tiny scores put every key within 1 of the row maximum: the lists cannot hold them, the CTAs
-    fall back to passes over score tiles, and the result is still the oracle's."""
+    """Tiny scores put every key in the support: no thread can hold its candidates, the CTAs fall back
+    to passes over score tiles, and the result is still the oracle's."""
     B, H, L, D, dtype = 1, 2, 4096, 128, torch.bfloat16
     q, k, v = (randn((B, H, L, D), dtype, s, scale=sc) for s, sc in ((1, 0.05), (2, 0.05), (3, 1.0)))
     read_status(q.device, reset=True)
+    set_flags(_lib.FLAG_CANDIDATE_LIST)
     out, tau, _, _, _ = entmax_attention_forward(q, k, v, 1.5, 10, True, None, use_block_mask=False)
     st = read_status(q.device)
     assert st["error"] == 0 and st["pass_ctas"] > 0, st
@@ -66,7 +67,7 @@ def test_list_overflow_falls_back_to_score_passes():
     assert maxdiff(tau, tau_ref) <= 5e-4
 
 
-@pytest.mark.parametrize("flags", [0, 1])
+@pytest.mark.parametrize("flags", [0, 1, 4])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("alpha", [1.5, 2.0])
 def test_backward_after_either_solver(flags, causal, alpha):

@@ -29,7 +29,7 @@ def _forward(lib, q, k, v, alpha, causal, use_tc):
         aux_s = torch.empty((B, H, L), dtype=torch.float32, device=q.device)
     rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), alpha, 10, tau.data_ptr(),
                                  aux_o.data_ptr() if aux_o is not None else None,
-                                 aux_s.data_ptr() if aux_s is not None else None, None, None, 0, _stream(q))
+                                 aux_s.data_ptr() if aux_s is not None else None, None, _stream(q))
     _lib.check(rc, "fla_entmax_attn_fwd")
     return g, tau, aux_o, aux_s
 
