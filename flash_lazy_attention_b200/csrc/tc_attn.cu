@@ -77,12 +77,11 @@ constexpr size_t bwd_smem_bytes() {   // Q, dO, the K slots, two V slots
 
 struct BwdMaps {
   CUtensorMap q, k, v, dout;   // 128-row boxes
-  CUtensorMap q64, do64;       // 64-row boxes (query sub-tiles of dkdv_kernel)
 };
 
 template <int D>
-constexpr size_t kv_smem_bytes() {
-  return (size_t)tc::TileCfg<D>::kTileBytes * (2 + tc::kKvStages) + 1024;
+constexpr size_t kv_smem_bytes() {   // K, V, two stages of (Q, dO)
+  return (size_t)tc::TileCfg<D>::kTileBytes * (2 + 2 * tc::kKvStages) + 1024;
 }
 
 template <int MODE, int D, int FMT, int KIND>
@@ -102,7 +101,7 @@ cudaError_t launch_bwd(const BwdMaps& m, const AttnParams& p, int* status, cudaS
   if (!FLA_DBG(p, 64)) kq<<<grid, tc::kBwdThreads, smem, st>>>(mq, mk, mv, mdo, p, status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  if (!FLA_DBG(p, 32)) kkv<<<grid, tc::kKvThreads, smem_kv, st>>>(m.q64, mk, mv, m.do64, p, status);
+  if (!FLA_DBG(p, 32)) kkv<<<grid, tc::kKvThreads, smem_kv, st>>>(mq, mk, mv, mdo, p, status);
   return cudaGetLastError();
 }
 
@@ -160,9 +159,7 @@ cudaError_t tc_attn_bwd(int mode, const AttnParams& p, int dtype, int* status, c
   if (!make_tensor_map_bhld(&m.q, p.q.ptr, p.B, p.H, p.L, p.D, p.q.s, 128, why) ||
       !make_tensor_map_bhld(&m.k, p.k.ptr, p.B, p.H, p.L, p.D, p.k.s, 128, why) ||
       !make_tensor_map_bhld(&m.v, p.v.ptr, p.B, p.H, p.L, p.D, p.v.s, 128, why) ||
-      !make_tensor_map_bhld(&m.dout, p.dout.ptr, p.B, p.H, p.L, p.D, p.dout.s, 128, why) ||
-      !make_tensor_map_bhld(&m.q64, p.q.ptr, p.B, p.H, p.L, p.D, p.q.s, 64, why) ||
-      !make_tensor_map_bhld(&m.do64, p.dout.ptr, p.B, p.H, p.L, p.D, p.dout.s, 64, why))
+      !make_tensor_map_bhld(&m.dout, p.dout.ptr, p.B, p.H, p.L, p.D, p.dout.s, 128, why))
     return cudaErrorNotSupported;
   return mode == ENTMAX ? launch_bwd_shape<ENTMAX>(m, p, dtype, status, st)
                         : launch_bwd_shape<LAZY>(m, p, dtype, status, st);
