@@ -202,6 +202,84 @@ def rows_table(steps, warmup):
             del x, dy, y
 
 
+def lazy_compare(steps, warmup):
+    """Same-box comparator for the Lazy Attention path: the reference's own Triton module, JIT-compiled for this
+    GPU (oracle/_ref/lazy_attention_triton.py, put there by oracle/make_ref.py), against this library on the same
+    bf16 inputs: forward + backward time with frozen and with trained bias / tau, and the largest difference
+    between the two implementations' outputs and gradients.  One JSON line per case."""
+    import torch
+
+    import flash_lazy_attention_b200 as fla
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "lazy_attention_triton.py")):
+        print(json.dumps({"lazy_compare": "unavailable", "why": "oracle/_ref/lazy_attention_triton.py is missing: "
+                          "run `python oracle/make_ref.py <reference checkout>` first"}), flush=True)
+        return
+    sys.path.insert(0, ref_dir)
+    try:
+        import lazy_attention_triton as ref_mod
+    except Exception as exc:   # Triton missing or unusable on this box
+        print(json.dumps({"lazy_compare": "unavailable", "why": f"{type(exc).__name__}: {exc}"}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+
+    def rope(x):
+        L, D = x.shape[-2], x.shape[-1]
+        half = D // 2
+        inv = 1.0 / (10000.0 ** (torch.arange(half, device=dev, dtype=torch.float32) / half))
+        ang = torch.arange(L, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+        return x * cos + torch.cat([-x[..., half:], x[..., :half]], -1) * sin
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    for name, (B, H, L, D, W) in (("B2 H8 L4096 D128 W512", (2, 8, 4096, 128, 512)),
+                                  ("config 4: B4 H32 L16384 D128 W512", (4, 32, 16384, 128, 512))):
+        gen = torch.Generator(device=dev).manual_seed(0)
+        q, k = (rope(torch.randn(B, H, L, D, generator=gen, device=dev)).to(torch.bfloat16) for _ in range(2))
+        v, do = (torch.randn(B, H, L, D, generator=gen, device=dev).to(torch.bfloat16) for _ in range(2))
+        bias = torch.randn(H, W, generator=gen, device=dev) * 0.02
+        tau = torch.full((H,), -1.0, device=dev)
+        F = 3.5 * flops_fwd(B, H, L, D, True)
+        for trained in (False, True):
+            def run(fn):
+                leaves = [t.detach().clone().requires_grad_(True) for t in (q, k, v)]
+                bp, tp = bias.clone().requires_grad_(trained), tau.clone().requires_grad_(trained)
+                out = fn(*leaves, bp.to(torch.bfloat16), tp.to(torch.bfloat16), window_size=W)
+                out.backward(do)
+                return [out.detach()] + [t.grad for t in leaves] + ([bp.grad, tp.grad] if trained else [])
+            line = {"lazy_compare": name, "trained_params": trained}
+            try:
+                ref_ms = timed(lambda: run(ref_mod.lazy_attention_triton))
+                ref_res = run(ref_mod.lazy_attention_triton)
+                line.update({"reference_triton_ms": ref_ms, "reference_triton_tflops": F / ref_ms / 1e9})
+            except Exception as exc:
+                ref_res = None
+                line["reference_triton"] = f"failed: {type(exc).__name__}: {str(exc)[:200]}"
+            ours_ms = timed(lambda: run(fla.lazy_attention_triton))
+            ours = run(fla.lazy_attention_triton)
+            line.update({"ours_ms": ours_ms, "ours_tflops": F / ours_ms / 1e9})
+            if ref_res is not None:
+                line["speedup"] = ref_ms / ours_ms
+                names = ["out", "dq", "dk", "dv", "dbias", "dtau"][:len(ours)]
+                line["max_abs_diff"] = {n: float((a.float() - b.float()).abs().max()) for n, a, b in zip(names, ours, ref_res)}
+                line["max_abs_ref"] = {n: float(b.float().abs().max()) for n, b in zip(names, ref_res)}
+            print(json.dumps(line), flush=True)
+            del ours, ref_res
+        del q, k, v, do
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -218,12 +296,22 @@ def main():
                     help="entmax workloads: q, k drawn around this many well separated centres in contiguous "
                          "segments of --seg tokens, so that most (query block, key block) pairs are empty")
     ap.add_argument("--seg", type=int, default=512, help="segment length of --clusters")
+    ap.add_argument("--partition", action="store_true",
+                    help="strong scaling: ONE seeded problem of the workload's size, its (batch, head) pairs split over "
+                         "the ranks (no collective in the timed region); afterwards the ranks' results are gathered "
+                         "over NCCL and rank 0 checks them bit for bit against its own unsharded run")
+    ap.add_argument("--lazy-compare", action="store_true",
+                    help="instead of the attention step: Lazy Attention of this library against the reference's Triton "
+                         "module on the same GPU (needs oracle/_ref, see oracle/make_ref.py)")
     ap.add_argument("--rows-table", action="store_true",
                     help="instead of the attention step: bandwidth of the stand-alone row entmax per shape")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.rows_table:
         rows_table(args.steps, args.warmup)
+        return
+    if args.lazy_compare:
+        lazy_compare(args.steps, args.warmup)
         return
 
     if args.impl == "reference":
@@ -275,7 +363,27 @@ def main():
             x = centres + 0.3 * x
         return x.to(torch.bfloat16)
 
-    q, k, v, do = (make(i) for i in range(4))
+    Bg, Hg = B, H                      # the global problem (partition mode shards it)
+    pieces = None
+    if args.partition:
+        if is_lazy or args.workload == "config3" or args.clusters:
+            raise SystemExit("--partition: entmax workloads without varlen only")
+        from flash_lazy_attention_b200.shard import bh_shard, gather_pairs, take_shard
+
+        def make_pairs(pairs):
+            """q, k, v, dO of the given (h, b) pairs, every pair from its own seed: [n, 1, L, D] each."""
+            outs = [[], [], [], []]
+            for (hh, bb) in pairs:
+                gp = torch.Generator(device=dev).manual_seed(100003 * hh + bb + 1)
+                for i in range(4):
+                    outs[i].append(torch.randn(1, 1, L, D, generator=gp, device=dev, dtype=torch.float32).to(torch.bfloat16))
+            return [torch.cat(o, dim=0) for o in outs]
+
+        pieces = bh_shard(Bg, Hg, rank, world)
+        q, k, v, do = make_pairs([(hh, bb) for (hh, b0, b1) in pieces for bb in range(b0, b1)])
+        B, H = q.shape[0], 1           # this rank's shard: every pair its own batch entry
+    else:
+        q, k, v, do = (make(i) for i in range(4))
     q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
     varlen = None
     if args.workload == "config3":
@@ -284,8 +392,9 @@ def main():
         bias = (torch.randn(H, 512, generator=gen, device=dev) * 0.02).requires_grad_(not args.frozen)
         tau_p = torch.full((H,), -1.0, device=dev).requires_grad_(not args.frozen)
     lens = varlen.double().cpu() if varlen is not None else torch.full((B,), float(L), dtype=torch.float64)
-    F_fwd = 4.0 * H * D * float((lens * lens).sum()) * (0.5 if causal else 1.0)
+    F_fwd = 4.0 * H * D * float((lens * lens).sum()) * (0.5 if causal else 1.0)   # of this rank's work
     F_step = 3.5 * F_fwd
+    F_job = 3.5 * flops_fwd(Bg, Hg, L, D, causal) if args.partition else world * F_step
 
     def forward():
         if is_lazy:
@@ -326,7 +435,38 @@ def main():
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    value = world * F_step / (ms * 1e-3) / 1e12
+    value = F_job / (ms * 1e-3) / 1e12
+
+    # ---- partition mode: gather the shards' results and compare with the unsharded run (outside any timing)
+    partition_check = None
+    if args.partition:
+        mine = [step().detach(), q.grad, k.grad, v.grad]
+        gathered = [gather_pairs(t, Bg, Hg) for t in mine] if world > 1 else None      # [Bg, Hg, L, D] on every rank
+        if rank == 0:
+            diffs = {}
+            if world > 1:
+                # rank 0 runs the whole problem itself, pair by pair in the same layout as its shards
+                worst = 0.0
+                identical = True
+                chunk = max(1, (Bg * Hg) // world)
+                allp = [(hh, bb) for hh in range(Hg) for bb in range(Bg)]
+                for c0 in range(0, len(allp), chunk):
+                    sub = allp[c0:c0 + chunk]
+                    fq, fk, fv, fdo = make_pairs(sub)
+                    fq.requires_grad_(True), fk.requires_grad_(True), fv.requires_grad_(True)
+                    fo = fla.adasplash(fq, fk, fv, alpha=alpha, niter=10, is_causal=causal)
+                    fo.backward(fdo)
+                    for name, full, ref in zip(("out", "dq", "dk", "dv"), gathered, (fo.detach(), fq.grad, fk.grad, fv.grad)):
+                        got = torch.stack([full[bb, hh] for (hh, bb) in sub]).unsqueeze(1)
+                        d = float((got.float() - ref.float()).abs().max())
+                        diffs[name] = max(diffs.get(name, 0.0), d)
+                        identical = identical and torch.equal(got, ref)
+                        worst = max(worst, d)
+                partition_check = {"bit_identical": identical, "max_abs_diff": diffs, "pairs": Bg * Hg,
+                                   "gathered_with": "NCCL all_gather (outside the timed region)"}
+            else:
+                partition_check = {"bit_identical": None, "note": "one rank: nothing to gather"}
+        del gathered
 
     # ---- per-kernel and per-phase timing, live ----------------------------------------------------------------
     # Phases: CUDA events between the two halves of whole steps, on the stream the library launches on.
@@ -494,9 +634,31 @@ def main():
         with torch.no_grad():
             chk = max(float((hout[B - 1:].to(dev).float() - out[B - 1:].float()).abs().max()),
                       float((hdq[B - 1:].to(dev).float() - q.grad[B - 1:].float()).abs().max()))
-        e2e = {"value": world * F_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+        # The same bytes with no kernel at all: q, k, v, dO host->device on one stream while out, dq, dk, dv go
+        # device->host on another (one cudaMemcpyAsync per tensor): the ceiling the host side allows this rank
+        # while all ranks copy at the same time.
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(n_e2e):
+            with torch.cuda.stream(s_in):
+                dq_.copy_(hq, non_blocking=True), dk_.copy_(hk, non_blocking=True)
+                dv_.copy_(hv, non_blocking=True), ddo_.copy_(hdo, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                hout.copy_(do, non_blocking=True), hdq.copy_(do, non_blocking=True)
+                hdk.copy_(do, non_blocking=True), hdv.copy_(do, non_blocking=True)
+        e2e_join()
+        c1.record()
+        barrier()
+        copy_ms = c0.elapsed_time(c1) / n_e2e
+        if world > 1:
+            t = torch.tensor([copy_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            copy_ms = float(t.item())
+        e2e = {"value": F_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes,
                "pipeline": f"{B} batch elements on three streams (copy in / compute / copy out)",
+               "copies_only_ms_per_step": copy_ms, "fraction_of_copies_only": copy_ms / e2e_ms,
                "max_abs_diff_vs_resident_step": chk}
 
     cpu = None
@@ -524,10 +686,13 @@ def main():
         # library kernels per step: forward, dQ, dK/dV (tensor-core family); the SIMT family adds the delta pre-pass
         launches_per_step = {"tcgen05": 3, "simt": 4}.get(path, 3)
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong" if args.partition else "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"{args.workload}: B={B} H={H} L={L} D={D} alpha={alpha} niter=10 causal={causal} "
-                                       f"per GPU, fwd+bwd, seeded N(0,1) q,k,v,dO",
+                "config": {"workload": (f"{args.workload}: B={Bg} H={Hg} L={L} D={D} alpha={alpha} niter=10 causal={causal} "
+                                        + ("in total, its (batch, head) pairs split over the GPUs" if args.partition else "per GPU")
+                                        + ", fwd+bwd, seeded N(0,1) q,k,v,dO"),
+                           "partition_check": partition_check,
                            "inputs": sparsity or "unstructured",
                            "kernel_family": path, "l2": "inputs larger than L2 (4 x %d MiB)" % (q.numel() * 2 >> 20),
                            "parallelism": f"(batch, head) shards on {world} GPU(s), no data-path collective"},

@@ -34,10 +34,10 @@ constexpr size_t fwd_smem_bytes() {   // Q, the K/V ring; entmax: staging slots 
   return (size_t)tc::TileCfg<D>::kTileBytes * (1 + tc::TileCfg<D>::kStages) + 1024 + (MODE == ENTMAX ? tc::kStageBytes : 0);
 }
 
-template <int MODE, int D, int FMT, int KIND>
+template <int MODE, int D, int FMT, int KIND, bool LISTS>
 cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        int* status, cudaStream_t st) {
-  auto kern = tc::fwd_kernel<MODE, D, FMT, KIND>;
+  auto kern = tc::fwd_kernel<MODE, D, FMT, KIND, LISTS>;
   constexpr size_t smem = fwd_smem_bytes<MODE, D>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
@@ -50,12 +50,20 @@ template <int MODE, int D, int FMT>
 cudaError_t launch_fwd_kind(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                             int* status, cudaStream_t st) {
   if constexpr (MODE == LAZY) {
-    return launch_fwd<MODE, D, FMT, 0>(mq, mk, mv, p, status, st);
+    return launch_fwd<MODE, D, FMT, 0, false>(mq, mk, mv, p, status, st);
   } else {
-    switch (alpha_kind(p.alpha)) {
-      case 0: return launch_fwd<MODE, D, FMT, 0>(mq, mk, mv, p, status, st);
-      case 1: return launch_fwd<MODE, D, FMT, 1>(mq, mk, mv, p, status, st);
-      default: return launch_fwd<MODE, D, FMT, 2>(mq, mk, mv, p, status, st);
+    // Thresholds iterated on kept candidates or by passes over score tiles: alpha = 2 defaults to the
+    // candidates, everything else to the passes (see the forward kernel); the flags override.
+    const int kind = alpha_kind(p.alpha);
+    const bool lists = (p.flags & FLA_FLAG_NO_CANDIDATE_LIST) ? false
+                                                               : (kind == 1 || (p.flags & FLA_FLAG_CANDIDATE_LIST) != 0);
+    switch (kind) {
+      case 0: return lists ? launch_fwd<MODE, D, FMT, 0, true>(mq, mk, mv, p, status, st)
+                           : launch_fwd<MODE, D, FMT, 0, false>(mq, mk, mv, p, status, st);
+      case 1: return lists ? launch_fwd<MODE, D, FMT, 1, true>(mq, mk, mv, p, status, st)
+                           : launch_fwd<MODE, D, FMT, 1, false>(mq, mk, mv, p, status, st);
+      default: return lists ? launch_fwd<MODE, D, FMT, 2, true>(mq, mk, mv, p, status, st)
+                            : launch_fwd<MODE, D, FMT, 2, false>(mq, mk, mv, p, status, st);
     }
   }
 }

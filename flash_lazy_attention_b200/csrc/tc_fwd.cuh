@@ -263,7 +263,10 @@ static __device__ __noinline__ TightenResult tighten_candidates(FwdShared* sh, f
   return r;
 }
 
-template <int MODE, int D, int FMT, int KIND>
+// LISTS: the entmax row-max pass keeps candidates and the thresholds are iterated on them (otherwise: by
+// passes over recomputed score tiles only).  A compile-time switch, because the candidate bookkeeping costs
+// the pass-only kernel registers it does not have.
+template <int MODE, int D, int FMT, int KIND, bool LISTS>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const AttnParams p, int* status) {
@@ -587,9 +590,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // threshold pass (three issue slots per score for the predicated store and pointer bump, plus the
         // tightening calls).  alpha = 2 pays that once instead of five or six Newton passes; alpha = 1.5,
         // whose tail-model first step gets by with three passes, comes out slightly behind and keeps the
-        // passes unless the caller asks for candidates.
-        bool lovf = p.niter <= 0 || (p.flags & FLA_FLAG_NO_CANDIDATE_LIST) != 0 ||
-                    (KIND != 1 && (p.flags & FLA_FLAG_CANDIDATE_LIST) == 0);
+        // passes unless the caller asks for candidates (the host side picks the kernel variant).
+        bool lovf = !LISTS || p.niter <= 0;
         float* const stage_t = reinterpret_cast<float*>(stage) + tid;  // slot x of this thread: stage_t[x * 512]
         const uint32_t sa0 = smem_u32(stage_t);
         uint32_t sa = sa0;
@@ -636,11 +638,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           }
           const float tm = fmaxf(m0, m1);
           mrow = fmaxf(mrow, tm);
-          rmx[quad * 128 + row] = mrow;
-          const float msh = fmaxf(fmaxf(rmx[row], rmx[128 + row]), fmaxf(rmx[256 + row], rmx[384 + row]));
+          float msh = mrow;   // largest score any of the row's four threads has seen (exchanged only while
+                              // candidates are kept: the filter gains from it, the tile marks hardly do)
+          if (LISTS && !lovf) {
+            rmx[quad * 128 + row] = mrow;
+            msh = fmaxf(fmaxf(rmx[row], rmx[128 + row]), fmaxf(rmx[256 + row], rmx[384 + row]));
+          }
           const bool near_max = tm > -INFINITY && (msh - tm) * c1 < 1.f;
           bool took = false;
-          if (!lovf && !FLA_DBG(p, 2048)) {
+          if (LISTS && !lovf && !FLA_DBG(p, 2048)) {
             // raw-score form of the row's best lower bound; masked entries are -inf and never pass
             const float blb = fmaxf(fmaxf(rlb[row], rlb[128 + row]), fmaxf(rlb[256 + row], rlb[384 + row]));
             const float thr = fmaxf(msh - inv_c1, blb * inv_c1);
@@ -671,11 +677,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           // One Newton step at the end of a tile keeps the published tangents fresh and the bound close to
           // the threshold of what the row has shown so far; the bound moves less and less, so the steps
           // thin out: after the thread's tiles 1-4, then 6, 8, 12, 16, 24, 32, ...
-          ++ntile;
-          {
+          if (LISTS && !lovf) {
+            ++ntile;
             const uint32_t third = ntile / 3u;
             const bool due = ntile <= 4u || (ntile & (ntile - 1u)) == 0u || (third * 3u == ntile && (third & (third - 1u)) == 0u);
-            if (!lovf && due) {
+            if (due) {
 #ifdef FLA_TRACE
               if (lane == 0 && status) atomicAdd(status + 21, 1);
 #endif
@@ -683,7 +689,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               tighten(1, 8);
             }
           }
-          mark_bits |= ((lovf ? near_max : took) ? 1u : 0u) << (kt & 31);
+          mark_bits |= (((!LISTS || lovf) ? near_max : took) ? 1u : 0u) << (kt & 31);
           TRACE((tid & 127) == 0 && half == 0, 1, kt, 7, trace_clock());
         });
         publish_marks();
@@ -701,7 +707,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           sh.act[1][lane] = nx;
           sh.act_next[lane] = 0u;
         }
-        const bool use_list = named_bar_and(2, kFwdRowThreads, !lovf);
+        const bool all_fit = named_bar_and(2, kFwdRowThreads, !lovf);
+        const bool use_list = LISTS && all_fit;
         m = live ? m * c1 : 0.f;
         const float n = (float)(jlim + 1);
         float ts = -1.f, lo = -1.f, hi = live ? -exp2f(-(p.alpha - 1.f) * log2f(fmaxf(n, 1.f))) : -1.f;
