@@ -3,6 +3,8 @@ from .ops import (adasplash, adasplash_no_block_mask, check_status, entmax_atten
                   last_call_info, lazy_attention_triton, read_status, set_flags, set_path, triton_entmax,
                   unpack_block_mask)
 
-__all__ = ["adasplash", "adasplash_no_block_mask", "triton_entmax", "lazy_attention_triton",
+from .layers import LazyAttention, LazyAttentionLayer  # noqa: F401,E402
+
+__all__ = ["LazyAttention", "LazyAttentionLayer", "adasplash", "adasplash_no_block_mask", "triton_entmax", "lazy_attention_triton",
            "entmax_attention_forward", "unpack_block_mask", "set_path", "last_call_info",
            "read_status", "check_status", "set_flags"]

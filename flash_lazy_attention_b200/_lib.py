@@ -25,7 +25,7 @@ class Tensor4(C.Structure):
 class AttnGeom(C.Structure):
     _fields_ = [("B", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("D", C.c_int32),
                 ("dtype", C.c_int32), ("causal", C.c_int32), ("varlen", C.c_void_p),
-                ("path", C.c_int32), ("status", C.c_void_p), ("flags", C.c_int32)]
+                ("path", C.c_int32), ("status", C.c_void_p), ("flags", C.c_int32), ("Hkv", C.c_int32)]
 
 
 _P4 = C.POINTER(Tensor4)

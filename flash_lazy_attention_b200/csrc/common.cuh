@@ -24,6 +24,7 @@ struct View4 {
 // One parameter block for every attention kernel (SIMT and tensor-core families).
 struct AttnParams {
   int B, H, L, D;
+  int Hkv, n_rep;   // grouped-query attention: k, v (and dk, dv) have Hkv = H / n_rep heads; query head h reads head h / n_rep
   int causal;
   const int* varlen;
   float scale;  // 1/sqrt(D)

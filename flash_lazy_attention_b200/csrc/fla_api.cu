@@ -108,6 +108,8 @@ static int check_geom(const fla_attn_geom* g) {
   if (g->D > 128) return fail(FLA_ERR_UNSUPPORTED, "head dim %d > 128 is not supported", g->D);
   if (g->path < FLA_PATH_AUTO || g->path > FLA_PATH_TCGEN05) return fail(FLA_ERR_INVALID, "unknown path %d", g->path);
   if ((int64_t)g->B > 65535 || (int64_t)g->H > 65535) return fail(FLA_ERR_UNSUPPORTED, "B and H must be <= 65535");
+  if (g->Hkv < 0 || (g->Hkv > 0 && (g->Hkv > g->H || g->H % g->Hkv != 0)))
+    return fail(FLA_ERR_INVALID, "Hkv = %d must divide H = %d", g->Hkv, g->H);
   return FLA_OK;
 }
 static int check_view(const fla_tensor4* t, const char* name, View4* out) {
@@ -123,6 +125,8 @@ static int check_view(const fla_tensor4* t, const char* name, View4* out) {
 static void fill_common(AttnParams& p, const fla_attn_geom* g) {
   memset(&p, 0, sizeof(p));
   p.B = g->B; p.H = g->H; p.L = g->L; p.D = g->D;
+  p.Hkv = g->Hkv > 0 ? g->Hkv : g->H;
+  p.n_rep = p.H / p.Hkv;
   p.causal = g->causal;
   p.varlen = g->varlen;
   p.scale = 1.0f / sqrtf((float)g->D);
@@ -149,6 +153,7 @@ static int dispatch(int mode, bool bwd, const fla_attn_geom* g, AttnParams& p, c
     if (e != cudaErrorNotSupported) return cuda_fail(e, "tensor-core launch");
     if (g->path == FLA_PATH_TCGEN05) return fail(FLA_ERR_UNSUPPORTED, "tensor-core path unavailable: %s", why);
   }
+  if (p.n_rep != 1) return fail(FLA_ERR_UNSUPPORTED, "shared k/v heads (Hkv < H) need the tensor-core family");
   if (bwd) {
     if (!p.aux_o || (mode == ENTMAX && !p.aux_s))
       return fail(FLA_ERR_INVALID, "the SIMT family needs the aux buffers its forward filled");
@@ -184,6 +189,7 @@ int fla_attn_uses_tensor_cores(const fla_attn_geom* g, const fla_tensor4* q, con
                                const fla_tensor4* v) {
   if (!g || !q || !k || !v || g->path == FLA_PATH_SIMT) return 0;
   if (g->B <= 0 || g->H <= 0 || g->L <= 0 || g->D <= 0) return 0;
+  if (g->Hkv < 0 || (g->Hkv > 0 && (g->Hkv > g->H || g->H % g->Hkv != 0))) return 0;
   AttnParams p;
   fill_common(p, g);
   View4* dst[3] = {&p.q, &p.k, &p.v};

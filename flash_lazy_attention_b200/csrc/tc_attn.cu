@@ -18,6 +18,10 @@ bool eligible(const AttnParams& p, int dtype, const char** why) {
   if ((int64_t)p.B * p.H * ((p.L + 127) / 128) > 0x7fffffffLL) { *why = "too many tiles"; return false; }
   if ((p.L + 63) / 64 > 32 * tc::kMaxMaskWords) { *why = "sequence too long for the block mask"; return false; }
   if ((p.L + 127) / 128 > tc::kBwdMaxTiles) { *why = "sequence too long for the backward tile list"; return false; }
+  if (p.n_rep > 64 || (int64_t)p.n_rep * ((p.L + 127) / 128) > tc::kKvMaxTiles) {
+    *why = "too many query heads per kv head for this sequence length";
+    return false;
+  }
   return true;
 }
 
@@ -104,12 +108,13 @@ cudaError_t launch_bwd(const BwdMaps& m, const AttnParams& p, int* status, cudaS
   e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
   if (e != cudaSuccess) return e;
   const unsigned grid = (unsigned)(((p.L + 127) / 128) * p.B * p.H);
+  const unsigned grid_kv = (unsigned)(((p.L + 127) / 128) * p.B * p.Hkv);   // one CTA per key tile of a kv head
   // dq_kernel first: its first sweep produces the row scalars delta that dkdv_kernel reads
   // (development builds can leave out one of the two launches for timing experiments)
   if (!FLA_DBG(p, 64)) kq<<<grid, tc::kBwdThreads, smem, st>>>(mq, mk, mv, mdo, p, status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  if (!FLA_DBG(p, 32)) kkv<<<grid, tc::kKvThreads, smem_kv, st>>>(mq, mk, mv, mdo, p, status);
+  if (!FLA_DBG(p, 32)) kkv<<<grid_kv, tc::kKvThreads, smem_kv, st>>>(mq, mk, mv, mdo, p, status);
   return cudaGetLastError();
 }
 
@@ -151,8 +156,8 @@ cudaError_t tc_attn_fwd(int mode, const AttnParams& p_in, int dtype, int* status
   if (!view_ok(p.q, why) || !view_ok(p.k, why) || !view_ok(p.v, why) || !view_ok(p.o, why)) return cudaErrorNotSupported;
   CUtensorMap mq, mk, mv;
   if (!make_tensor_map_bhld(&mq, p.q.ptr, p.B, p.H, p.L, p.D, p.q.s, 128, why) ||
-      !make_tensor_map_bhld(&mk, p.k.ptr, p.B, p.H, p.L, p.D, p.k.s, 128, why) ||
-      !make_tensor_map_bhld(&mv, p.v.ptr, p.B, p.H, p.L, p.D, p.v.s, 128, why))
+      !make_tensor_map_bhld(&mk, p.k.ptr, p.B, p.Hkv, p.L, p.D, p.k.s, 128, why) ||
+      !make_tensor_map_bhld(&mv, p.v.ptr, p.B, p.Hkv, p.L, p.D, p.v.s, 128, why))
     return cudaErrorNotSupported;
   return mode == ENTMAX ? launch_fwd_shape<ENTMAX>(mq, mk, mv, p, dtype, status, st)
                         : launch_fwd_shape<LAZY>(mq, mk, mv, p, dtype, status, st);
@@ -165,8 +170,8 @@ cudaError_t tc_attn_bwd(int mode, const AttnParams& p, int dtype, int* status, c
     return cudaErrorNotSupported;
   BwdMaps m;
   if (!make_tensor_map_bhld(&m.q, p.q.ptr, p.B, p.H, p.L, p.D, p.q.s, 128, why) ||
-      !make_tensor_map_bhld(&m.k, p.k.ptr, p.B, p.H, p.L, p.D, p.k.s, 128, why) ||
-      !make_tensor_map_bhld(&m.v, p.v.ptr, p.B, p.H, p.L, p.D, p.v.s, 128, why) ||
+      !make_tensor_map_bhld(&m.k, p.k.ptr, p.B, p.Hkv, p.L, p.D, p.k.s, 128, why) ||
+      !make_tensor_map_bhld(&m.v, p.v.ptr, p.B, p.Hkv, p.L, p.D, p.v.s, 128, why) ||
       !make_tensor_map_bhld(&m.dout, p.dout.ptr, p.B, p.H, p.L, p.D, p.dout.s, 128, why))
     return cudaErrorNotSupported;
   return mode == ENTMAX ? launch_bwd_shape<ENTMAX>(m, p, dtype, status, st)

@@ -203,10 +203,10 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         // sweep), the V half after the dP product: each is refilled as soon as its own reader is done
         if (!mbar_wait(&sh.k_empty[ks], k_phase(g) ^ 1u, abort_flag, status, 40)) break;
         mbar_expect_tx(&sh.k_full[ks], Cfg::kTileBytes);
-        tma_load_tile<D>(ring + ks * Cfg::kTileBytes, &map_k, &sh.k_full[ks], kt * 128, h, b);
+        tma_load_tile<D>(ring + ks * Cfg::kTileBytes, &map_k, &sh.k_full[ks], kt * 128, h / p.n_rep, b);   // (kv head)
         if (!mbar_wait(&sh.v_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, status, 40)) break;
         mbar_expect_tx(&sh.v_full[s], Cfg::kTileBytes);
-        tma_load_tile<D>(ring + (NK + s) * Cfg::kTileBytes, &map_v, &sh.v_full[s], kt * 128, h, b);
+        tma_load_tile<D>(ring + (NK + s) * Cfg::kTileBytes, &map_v, &sh.v_full[s], kt * 128, h / p.n_rep, b);
       }
     }
     __syncwarp();

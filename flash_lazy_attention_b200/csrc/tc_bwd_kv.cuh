@@ -1,7 +1,8 @@
 // Tensor-core dK / dV kernel of alpha-entmax attention and Lazy Attention.
 //
-// One CTA per 128-key tile; K and V stay in shared memory, (Q, dO) tiles of 128 query rows stream
-// through a two-stage ring.  Scores are produced transposed (S^T = K.Q^T, dP^T = V.dO^T, 128 keys x
+// One CTA per 128-key tile of one (batch, kv head); K and V stay in shared memory, the (Q, dO) tiles of
+// 128 query rows of every query head that shares this kv head (one without grouped-query attention)
+// stream through a two-stage ring and accumulate into the same dK and dV.  Scores are produced transposed (S^T = K.Q^T, dP^T = V.dO^T, 128 keys x
 // 128 queries, one N = 128 product each) so that a thread owns a key row; per-query statistics (tau or
 // lse, delta, tau_h/(i+1)) are staged in shared memory.
 //
@@ -38,6 +39,7 @@ constexpr int kKvRowWarps = 16;
 constexpr int kKvProducerWarp = 16;
 constexpr int kKvMmaWarp = 17;
 constexpr int kKvStages = 2;
+constexpr int kKvMaxTiles = 2048;   // (query head of the group, query tile) items per CTA
 
 struct KvShared {
   uint64_t res_full, ring_full[kKvStages], ring_empty[kKvStages];
@@ -45,8 +47,8 @@ struct KvShared {
   uint32_t tmem_base;
   int abort_flag;
   float stat[2][3][128];     // double buffer, statistic, query column
-  int nact;                  // number of query tiles this CTA visits
-  uint16_t tiles[kBwdMaxTiles];   // their indices (128-row units), ascending
+  int nact;                  // number of (query head, query tile) items this CTA visits
+  uint16_t tiles[kKvMaxTiles];    // query tile (128-row units) in the low 9 bits, head of the group above
 };
 
 // D[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory as four pieces of 16 columns (16-bit
@@ -84,9 +86,9 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   // stream the same Q/dO tensors out of the L2 cache; key tile 0 sees every query tile under the
   // causal mask: heaviest first
   const int nkt_grid = (L + 127) >> 7;
-  const int bh = (int)(blockIdx.x / nkt_grid);
+  const int bhk = (int)(blockIdx.x / nkt_grid);
   const int nt = (int)(blockIdx.x % nkt_grid);
-  const int b = bh / p.H, h = bh % p.H;
+  const int b = bhk / p.Hkv, hk = bhk % p.Hkv;     // kv head; its query heads are hk * n_rep + rep
   const int len = p.varlen ? min(max(p.varlen[b], 0), L) : L;
   const int col0 = nt * 128;
   const bool tile_live = col0 < len;
@@ -110,20 +112,23 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     fence_mbar_init();
   }
   if (warp == 0) {
-    // query tiles to visit: all, or those with a non-zero probability in one of the two 64-key
-    // halves of this key tile according to the forward's block mask
+    // items to visit: every query tile of every query head of the group, or those with a non-zero
+    // probability in one of the two 64-key halves of this key tile according to the forward's block mask
     int n = 0;
     const int nmt = (L + 127) >> 7;
-    for (int base = 0; base < nq_all; base += 32) {
-      const int qt = qt_begin + base + lane;
-      bool on = base + lane < nq_all;
-      if (on && p.block_mask != nullptr) {
-        const uint32_t w = p.block_mask[((int64_t)bh * nmt + qt) * p.mask_words + ((2 * nt) >> 5)];
-        on = ((w >> ((2 * nt) & 31)) & 3u) != 0u;
+    for (int rep = 0; rep < p.n_rep; ++rep) {
+      const int64_t bh = (int64_t)b * p.H + hk * p.n_rep + rep;
+      for (int base = 0; base < nq_all; base += 32) {
+        const int qt = qt_begin + base + lane;
+        bool on = base + lane < nq_all;
+        if (on && p.block_mask != nullptr) {
+          const uint32_t w = p.block_mask[(bh * nmt + qt) * p.mask_words + ((2 * nt) >> 5)];
+          on = ((w >> ((2 * nt) & 31)) & 3u) != 0u;
+        }
+        const uint32_t votes = __ballot_sync(0xffffffffu, on);
+        if (on) sh.tiles[n + __popc(votes & ((1u << lane) - 1u))] = (uint16_t)((rep << 9) | qt);
+        n += __popc(votes);
       }
-      const uint32_t votes = __ballot_sync(0xffffffffu, on);
-      if (on) sh.tiles[n + __popc(votes & ((1u << lane) - 1u))] = (uint16_t)qt;
-      n += __popc(votes);
     }
     if (lane == 0) sh.nact = n;
   }
@@ -139,10 +144,10 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     if (lane == 0 && tile_live) {
       tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); tma_prefetch_desc(&map_do);
       mbar_expect_tx(&sh.res_full, 2 * Cfg::kTileBytes);
-      tma_load_tile<D>(sK, &map_k, &sh.res_full, col0, h, b);
-      tma_load_tile<D>(sV, &map_v, &sh.res_full, col0, h, b);
+      tma_load_tile<D>(sK, &map_k, &sh.res_full, col0, hk, b);
+      tma_load_tile<D>(sV, &map_v, &sh.res_full, col0, hk, b);
       for (int n = 0; n < nq; ++n) {
-        const int s = n % kKvStages, q0 = (int)sh.tiles[n] * 128;
+        const int s = n % kKvStages, q0 = (int)(sh.tiles[n] & 511u) * 128, h = hk * p.n_rep + (int)(sh.tiles[n] >> 9);
         uint8_t* dst = ring + s * 2 * Cfg::kTileBytes;
         if (!mbar_wait(&sh.ring_empty[s], ((n / kKvStages) & 1) ^ 1, abort_flag, status, 60)) break;
         mbar_expect_tx(&sh.ring_full[s], 2 * Cfg::kTileBytes);
@@ -190,7 +195,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
           // query rows beyond the end of the sequence: padding rows of Q and dO stay out of the
           // reductions (the score products of this tile have completed), see zero_tail_rows
           int nks = 8;
-          const int valid = len - (int)sh.tiles[n] * 128;
+          const int valid = len - (int)(sh.tiles[n] & 511u) * 128;
           if (ok && valid < 128) {
             uint8_t* stage = ring + s * 2 * Cfg::kTileBytes;
             zero_tail_rows(stage, valid, Cfg::kBoxes, 128);
@@ -219,12 +224,10 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     // my 32 score columns; P^T / dS^T (16-bit pairs) go to the first 16 of them
     const uint32_t t_s = tmem + lane_base + quad * 32, t_dp = t_s + 128;
-    const int64_t bhl = (int64_t)bh * L;
     if (tile_live) {
       const float c1 = p.scale * (MODE == ENTMAX ? (p.alpha - 1.f) : kLog2e);
       const float e = MODE == ENTMAX ? 1.f / (p.alpha - 1.f) : 0.f;
-      const float* gstat = (MODE == ENTMAX ? p.tau : p.lse) + bhl;
-      const float tau_head = MODE == LAZY ? p.tau_h[h] : 0.f;
+      const float* gstat = MODE == ENTMAX ? p.tau : p.lse;
       // The statistics of a tile's 128 query rows are fetched one tile ahead (threads 0-127, one row
       // each): the loads from global memory are in flight while the previous tile is worked on.
       // entmax keeps the negated values: they are the addends of  x = s*c1 - tau  and  dP - delta.
@@ -232,20 +235,22 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       float nx_stat = 0.f, nx_delta = 0.f;
       auto fetch_stats = [&](int n) {
         if (tid < 128 && n < nq) {
-          const int qi = (int)sh.tiles[n] * 128 + tid;
+          const int qi = (int)(sh.tiles[n] & 511u) * 128 + tid;
+          const int64_t bhl = ((int64_t)b * p.H + hk * p.n_rep + (int)(sh.tiles[n] >> 9)) * L;
           const bool ql = qi < len;
-          nx_stat = ql ? sgn * gstat[qi] : 0.f;
+          nx_stat = ql ? sgn * gstat[bhl + qi] : 0.f;
           nx_delta = ql ? sgn * p.delta[bhl + qi] : 0.f;
         }
       };
       fetch_stats(0);
       for (int n = 0; n < nq; ++n) {
-        const int q0 = (int)sh.tiles[n] * 128;
+        const int q0 = (int)(sh.tiles[n] & 511u) * 128;
+        const int h = hk * p.n_rep + (int)(sh.tiles[n] >> 9);    // query head of this item
         float (*st)[128] = sh.stat[n & 1];
         if (tid < 128) {
           st[0][tid] = nx_stat;
           st[1][tid] = nx_delta;
-          st[2][tid] = MODE == LAZY ? tau_head / (float)(q0 + tid + 1) : 0.f;
+          st[2][tid] = MODE == LAZY ? p.tau_h[h] / (float)(q0 + tid + 1) : 0.f;
         }
         fetch_stats(n + 1);
         named_bar_sync(1, kKvRowThreads);
@@ -369,7 +374,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       // quads 0, 1 store dK, quads 2, 3 store dV; each takes half of the columns
       const int grp = quad >> 1, half = quad & 1;
       uint8_t* grow = (uint8_t*)(grp == 0 ? p.dk.ptr : p.dv.ptr) +
-                      2 * ((int64_t)b * (grp == 0 ? p.dk.s[0] : p.dv.s[0]) + (int64_t)h * (grp == 0 ? p.dk.s[1] : p.dv.s[1]) +
+                      2 * ((int64_t)b * (grp == 0 ? p.dk.s[0] : p.dv.s[0]) + (int64_t)hk * (grp == 0 ? p.dk.s[1] : p.dv.s[1]) +
                            (int64_t)j * (grp == 0 ? p.dk.s[2] : p.dv.s[2]));
       const float mul = grp == 0 ? p.scale : 1.f;
 #pragma unroll
@@ -392,7 +397,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     } else if (j < L) {
       const int grp = quad >> 1, half = quad & 1;
       uint8_t* grow = (uint8_t*)(grp == 0 ? p.dk.ptr : p.dv.ptr) +
-                      2 * ((int64_t)b * (grp == 0 ? p.dk.s[0] : p.dv.s[0]) + (int64_t)h * (grp == 0 ? p.dk.s[1] : p.dv.s[1]) +
+                      2 * ((int64_t)b * (grp == 0 ? p.dk.s[0] : p.dv.s[0]) + (int64_t)hk * (grp == 0 ? p.dk.s[1] : p.dv.s[1]) +
                            (int64_t)j * (grp == 0 ? p.dk.s[2] : p.dv.s[2]));
 #pragma unroll
       for (int x = 0; x < D / 2; x += 8) *(uint4*)(grow + (half * (D / 2) + x) * 2) = make_uint4(0u, 0u, 0u, 0u);

@@ -392,7 +392,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t st = rp.stage();
         if (!mbar_wait(&sh.ring_empty[st], rp.phase() ^ 1u, abort_flag, status, tag)) return;
         mbar_expect_tx(&sh.ring_full[st], Cfg::kTileBytes);
-        tma_load_tile<D>(ring + st * Cfg::kTileBytes, map, &sh.ring_full[st], kt * 128, h, b);
+        tma_load_tile<D>(ring + st * Cfg::kTileBytes, map, &sh.ring_full[st], kt * 128, h / p.n_rep, b);   // (kv head)
         rp.advance();
       };
       while (true) {  // score-only passes
@@ -793,6 +793,64 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             }
             // (the barrier also orders this iteration's reads of the partial sums before the next writes)
             if (named_bar_and(2, kFwdRowThreads, done || *abort_flag != 0)) break;
+          }
+          // Canonical finish (alpha = 1.5 and 2).  Which candidates a thread still holds, the point the
+          // iteration started from and the order of the pool depend on how the warps happened to interleave,
+          // so the converged threshold differs from run to run in its last bits -- enough to flip an entry
+          // sitting on the threshold and, with it, a whole row of gradients (the entmax Jacobian jumps where
+          // the support changes).  The iteration is therefore only trusted to identify the support; the
+          // threshold is then recomputed from it in closed form, from sums formed as integers (order does
+          // not matter) of z = X - max rounded to 2^-24:  alpha = 2: tau = (sum z - 1) / n;  alpha = 1.5:
+          // the smaller root of  n tau^2 - 2 tau sum z + sum z^2 - 1 = 0.  Same support, same bits.
+          if (KIND != 2 && !*abort_flag) {
+            long long zs1 = 0, zs2 = 0;
+            int zn = 0;
+            const float noff = -(m + ts);
+            auto take = [&](float sv) {
+              if (fmaf(sv, c1, noff) > 0.f) {
+                const long long zi = __float2ll_rn(fmaf(sv, c1, -m) * 16777216.f);
+                zs1 += zi;
+                if (KIND == 0) zs2 += zi * zi;
+                ++zn;
+              }
+            };
+            for (int j = 0; j < n_st; ++j) take(stage_t[j * kFwdRowThreads]);
+            for (int i2 = quad; i2 < npool; i2 += 4) {
+              const float2 pe = sh.pool[i2];
+              if (__float_as_int(pe.y) == row) take(pe.x);
+            }
+            // the four threads of a row exchange through their own first candidate slots (all read by now)
+            uint32_t* const xs = reinterpret_cast<uint32_t*>(stage_t);
+            xs[0] = (uint32_t)zn;
+            xs[1 * kFwdRowThreads] = (uint32_t)(unsigned long long)zs1;
+            xs[2 * kFwdRowThreads] = (uint32_t)((unsigned long long)zs1 >> 32);
+            xs[3 * kFwdRowThreads] = (uint32_t)(unsigned long long)zs2;
+            xs[4 * kFwdRowThreads] = (uint32_t)((unsigned long long)zs2 >> 32);
+            named_bar_sync(1, kFwdRowThreads);
+            long long t1 = 0, t2 = 0;
+            int tn = 0;
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) {
+              // thread `qq` of this row: warp (row / 32) + 4 (qq / 2) + 8 (qq % 2), same lane
+              const uint32_t* xo = reinterpret_cast<const uint32_t*>(stage) + (((row >> 5) + 4 * (qq >> 1) + 8 * (qq & 1)) * 32 + (row & 31));
+              tn += (int)xo[0];
+              t1 += (long long)((unsigned long long)xo[1 * kFwdRowThreads] | ((unsigned long long)xo[2 * kFwdRowThreads] << 32));
+              t2 += (long long)((unsigned long long)xo[3 * kFwdRowThreads] | ((unsigned long long)xo[4 * kFwdRowThreads] << 32));
+            }
+            if (live && tn > 0) {
+              const double zsum = (double)t1 * (1.0 / 16777216.0), nd = (double)tn;
+              double zt;
+              if (KIND == 1) {
+                zt = (zsum - 1.0) / nd;
+              } else {
+                const double zsq = (double)t2 * (1.0 / 16777216.0 / 16777216.0);
+                const double disc = zsum * zsum - nd * (zsq - 1.0);
+                zt = (zsum - sqrt(fmax(disc, 0.0))) / nd;
+              }
+              // (taken only if it agrees with the iteration: it cannot differ by more than rounding unless
+              // an entry sat on the threshold or the iteration was cut short by niter)
+              if (fabs(zt - (double)ts) <= 1e-4) ts = (float)zt;
+            }
           }
           TRACE_PASS(29);
         } else {

@@ -120,7 +120,7 @@ def check_status(device=None) -> None:
     _lib.check(rc, "fla_check_status")
 
 
-def _geom(q: torch.Tensor, causal: bool, varlen32) -> AttnGeom:
+def _geom(q: torch.Tensor, causal: bool, varlen32, kv_heads: int = 0) -> AttnGeom:
     B, H, L, D = q.shape
     g = AttnGeom()
     g.B, g.H, g.L, g.D = B, H, L, D
@@ -130,6 +130,7 @@ def _geom(q: torch.Tensor, causal: bool, varlen32) -> AttnGeom:
     g.path = _path()
     g.status = _status_buf(q.device).data_ptr()
     g.flags = _flags
+    g.Hkv = int(kv_heads)
     return g
 
 
@@ -151,9 +152,26 @@ def _qkv_checked(q, k, v):
         _check_cuda(t, n)
         if t.dim() != 4:
             raise ValueError(f"{n} must be [B, H, L, D]")
-    if not (q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype):
-        raise ValueError("q, k, v must share shape and dtype")
+    if not (k.shape == v.shape and q.dtype == k.dtype == v.dtype):
+        raise ValueError("k and v must share their shape, and q, k, v their dtype")
+    if q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:] or k.shape[1] < 1 or q.shape[1] % k.shape[1] != 0:
+        raise ValueError("k, v must be [B, Hkv, L, D] with Hkv dividing the H of q [B, H, L, D]")
     return _unit_inner(q), _unit_inner(k), _unit_inner(v)
+
+
+def _shared_kv(lib, q, k, v, causal, vl):
+    """Grouped-query attention: k, v with fewer heads than q.  The tensor-core kernels read the shared heads
+    in place (query head h uses head h // (H // Hkv)); where they cannot take the call, the heads are repeated
+    here (what the reference's layers always do, examples/sw_attention_lazy.py:30-41) and autograd sums the
+    gradients of the copies.  Returns (k, v, kv_heads for the geometry)."""
+    H, Hkv = q.shape[1], k.shape[1]
+    if Hkv == H:
+        return k, v, 0
+    with torch.cuda.device(q.device):
+        if lib.fla_attn_uses_tensor_cores(_geom(q, causal, vl, Hkv), _t4(q), _t4(k), _t4(v)):
+            return k, v, Hkv
+    n_rep = H // Hkv
+    return k.repeat_interleave(n_rep, dim=1), v.repeat_interleave(n_rep, dim=1), 0
 
 
 # ---------------------------------------------------------------------------------------------
@@ -161,13 +179,13 @@ def _qkv_checked(q, k, v):
 # ---------------------------------------------------------------------------------------------
 class EntmaxAttnFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, alpha, niter, is_causal, varlen, use_block_mask):
+    def forward(ctx, q, k, v, alpha, niter, is_causal, varlen, use_block_mask, kv_heads=0):
         lib = _lib.load()
         q, k, v = _qkv_checked(q, k, v)
         B, H, L, D = q.shape
         vl = _varlen32(varlen, q)
         with torch.cuda.device(q.device):
-            g = _geom(q, is_causal, vl)
+            g = _geom(q, is_causal, vl, kv_heads)
             # only the SIMT family's backward needs the aux buffers
             need_aux = any(ctx.needs_input_grad[:3]) and not lib.fla_attn_uses_tensor_cores(g, _t4(q), _t4(k), _t4(v))
             out = torch.empty((B, H, L, D), dtype=q.dtype, device=q.device)
@@ -184,7 +202,7 @@ class EntmaxAttnFunc(torch.autograd.Function):
                                          mask.data_ptr() if mask is not None else None, _stream(q))
             _lib.check(rc, "fla_entmax_attn_fwd")
         ctx.save_for_backward(q, k, v, tau, aux_o, aux_s, mask, vl)
-        ctx.alpha, ctx.is_causal = float(alpha), bool(is_causal)
+        ctx.alpha, ctx.is_causal, ctx.kv_heads = float(alpha), bool(is_causal), int(kv_heads)
         ctx.block_mask = mask
         return out
 
@@ -194,8 +212,9 @@ class EntmaxAttnFunc(torch.autograd.Function):
         q, k, v, tau, aux_o, aux_s, mask, vl = ctx.saved_tensors
         do = _tma_friendly(do)
         with torch.cuda.device(q.device):
-            dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
-            g = _geom(q, ctx.is_causal, vl)
+            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            dk, dv = (torch.empty(k.shape, dtype=q.dtype, device=q.device) for _ in range(2))
+            g = _geom(q, ctx.is_causal, vl, ctx.kv_heads)
             nbytes = lib.fla_entmax_attn_bwd_workspace(g)
             ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
             rc = lib.fla_entmax_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(do), ctx.alpha, tau.data_ptr(),
@@ -204,17 +223,26 @@ class EntmaxAttnFunc(torch.autograd.Function):
                                          mask.data_ptr() if mask is not None else None,
                                          _t4(dq), _t4(dk), _t4(dv), ws.data_ptr(), nbytes, _stream(q))
             _lib.check(rc, "fla_entmax_attn_bwd")
-        return dq, dk, dv, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def _entmax_attn(q, k, v, alpha, niter, is_causal, varlen, use_block_mask):
+    if k.dim() == 4 and q.dim() == 4 and k.shape[1] != q.shape[1] and q.is_cuda:
+        q_, k_, v_ = _qkv_checked(q, k, v)
+        k, v, kvh = _shared_kv(_lib.load(), q_, k_, v_, is_causal, _varlen32(varlen, q_))
+        return EntmaxAttnFunc.apply(q, k, v, alpha, niter, is_causal, varlen, use_block_mask, kvh)
+    return EntmaxAttnFunc.apply(q, k, v, alpha, niter, is_causal, varlen, use_block_mask, 0)
 
 
 def adasplash(q, k, v, alpha=1.5, niter=10, is_causal=False, varlen=None):
-    """Block-masked alpha-entmax flash attention, forward + backward."""
-    return EntmaxAttnFunc.apply(q, k, v, alpha, niter, is_causal, varlen, True)
+    """Block-masked alpha-entmax flash attention, forward + backward.  k, v may have fewer heads than q
+    (grouped-query attention: Hkv dividing H)."""
+    return _entmax_attn(q, k, v, alpha, niter, is_causal, varlen, True)
 
 
 def adasplash_no_block_mask(q, k, v, alpha=1.5, niter=10, is_causal=False, varlen=None):
     """Same mathematics without the block bitmask (less memory, every block visited)."""
-    return EntmaxAttnFunc.apply(q, k, v, alpha, niter, is_causal, varlen, False)
+    return _entmax_attn(q, k, v, alpha, niter, is_causal, varlen, False)
 
 
 def entmax_attention_forward(q, k, v, alpha=1.5, niter=10, is_causal=False, varlen=None,
@@ -257,7 +285,7 @@ def unpack_block_mask(mask: torch.Tensor, L: int) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 class LazyAttentionFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, bias, tau, window_size, varlen=None):
+    def forward(ctx, q, k, v, bias, tau, window_size, varlen=None, kv_heads=0):
         lib = _lib.load()
         q, k, v = _qkv_checked(q, k, v)
         B, H, L, D = q.shape
@@ -270,7 +298,7 @@ class LazyAttentionFunc(torch.autograd.Function):
         bias32 = bias.detach().to(device=q.device, dtype=torch.float32).contiguous()
         tau32 = tau.detach().to(device=q.device, dtype=torch.float32).contiguous().view(-1)
         with torch.cuda.device(q.device):
-            g = _geom(q, True, vl)
+            g = _geom(q, True, vl, kv_heads)
             need_aux = any(ctx.needs_input_grad[:5]) and not lib.fla_attn_uses_tensor_cores(g, _t4(q), _t4(k), _t4(v))
             out = torch.empty((B, H, L, D), dtype=q.dtype, device=q.device)
             lse = torch.empty((B, H, L), dtype=torch.float32, device=q.device)
@@ -280,7 +308,7 @@ class LazyAttentionFunc(torch.autograd.Function):
                                        aux_o.data_ptr() if need_aux else None, _stream(q))
             _lib.check(rc, "fla_lazy_attn_fwd")
         ctx.save_for_backward(q, k, v, out, bias32, tau32, lse, aux_o, vl)
-        ctx.window = window
+        ctx.window, ctx.kv_heads = window, int(kv_heads)
         ctx.bias_shape, ctx.tau_shape = tuple(bias.shape), tuple(tau.shape)
         return out
 
@@ -292,12 +320,13 @@ class LazyAttentionFunc(torch.autograd.Function):
         H = q.shape[1]
         want_params = ctx.needs_input_grad[3] or ctx.needs_input_grad[4]
         with torch.cuda.device(q.device):
-            dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            dk, dv = (torch.empty(k.shape, dtype=q.dtype, device=q.device) for _ in range(2))
             dbias = dtau = None
             if want_params:  # fp32 like the reference (lazy_attention_triton.py:532-533)
                 dbias = torch.zeros(ctx.bias_shape, dtype=torch.float32, device=q.device)
                 dtau = torch.zeros((H,), dtype=torch.float32, device=q.device)
-            g = _geom(q, True, vl)
+            g = _geom(q, True, vl, ctx.kv_heads)
             nbytes = lib.fla_lazy_attn_bwd_workspace(g)
             ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
             rc = lib.fla_lazy_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(out), _t4(do), bias32.data_ptr(),
@@ -310,15 +339,20 @@ class LazyAttentionFunc(torch.autograd.Function):
             _lib.check(rc, "fla_lazy_attn_bwd")
         if want_params:
             dtau = dtau.view(ctx.tau_shape)
-        return dq, dk, dv, dbias, dtau, None, None
+        return dq, dk, dv, dbias, dtau, None, None, None
 
 
 def lazy_attention_triton(q, k, v, bias, tau, window_size=None, varlen=None):
     """Lazy Attention: scores + windowed head-wise bias, softmax, ReLU(P + tau/i), times V.
-    ``window_size`` defaults to ``bias.shape[1]`` (lazy_attention_triton.py:503-507)."""
+    ``window_size`` defaults to ``bias.shape[1]`` (lazy_attention_triton.py:503-507).  k, v may have fewer
+    heads than q (grouped-query attention: Hkv dividing H); bias and tau are per query head."""
     if window_size is None:
         window_size = bias.shape[1]
-    return LazyAttentionFunc.apply(q, k, v, bias, tau, window_size, varlen)
+    kvh = 0
+    if k.dim() == 4 and q.dim() == 4 and k.shape[1] != q.shape[1] and q.is_cuda:
+        q_, k_, v_ = _qkv_checked(q, k, v)
+        k, v, kvh = _shared_kv(_lib.load(), q_, k_, v_, True, _varlen32(varlen, q_))
+    return LazyAttentionFunc.apply(q, k, v, bias, tau, window_size, varlen, kvh)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -79,6 +79,10 @@ typedef struct fla_attn_geom {
                            * set): the live per-kernel durations of the benchmark.  Never cleared  *
                            * by the library; the caller zeroes it.                                */
   int32_t flags;          /* FLA_FLAG_*                                                         */
+  int32_t Hkv;            /* grouped-query attention: k, v, dk, dv are [B,Hkv,L,D] views and query  *
+                           * head h uses head h / (H / Hkv) of them; 0 or H: every query head its  *
+                           * own (the reference materialises the repeat: repeat_kv,                *
+                           * examples/sw_attention_lazy.py:30-41,154-157).  Tensor-core family only. */
 } fla_attn_geom;
 
 /* Library / ABI version (major*1000 + minor). */
