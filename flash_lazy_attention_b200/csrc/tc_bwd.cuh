@@ -24,10 +24,10 @@
 namespace fla {
 namespace tc {
 
-constexpr int kBwdThreads = 384;
-constexpr int kBwdRowThreads = 256;   // warps 0-7, two threads per tile row
-constexpr int kBwdRowWarps = 8;
-constexpr int kBwdProducerWarp = 8;   // warps 9, 10 and 11 issue the products
+constexpr int kBwdThreads = 640;
+constexpr int kBwdRowThreads = 512;   // warps 0-15, four threads per tile row
+constexpr int kBwdRowWarps = 16;
+constexpr int kBwdProducerWarp = 16;  // warps 17, 18 and 19 issue the products
 constexpr int kDbiasSmem = 2048;  // window distances accumulated in shared memory per CTA
 
 constexpr int kBwdMaxTiles = 512;     // key tiles per row of the tile list: L <= 65536
@@ -93,32 +93,34 @@ __device__ __forceinline__ void prob_terms(float x, float e, float tau_row, bool
 #define DQTRACE(cond, idx, slot) do { } while (0)
 #endif
 
-// dQ[128 x D] (+)= dS[128 x 128] . K[128 x D] with the 16-bit dS operand in two pieces of tensor
-// memory: keys 0-63 in columns [0, 32) of the buffer, keys 64-127 in columns [64, 96).
-// `nks`: 16-key steps to issue (fewer than 8 for the tile that reaches into a sequence's padding).
+// D[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory as four pieces of 16 columns (16-bit
+// pairs), piece q at a_tmem + 32 q (each of the four threads of a row writes its 32 reduction elements inside
+// the columns it read); B a [128 rows x D] tile whose rows are the reduction dimension.  `nks`: 16-row steps
+// to issue (fewer than 8 for the tile that reaches into a sequence's padding).
 template <int D, int FMT>
-__device__ __forceinline__ void issue_tn_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
+__device__ __forceinline__ void issue_tn_quads(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
                                                int nks = 8) {
-  constexpr uint32_t idesc = make_idesc2(128, D, FMT, FMT, 0, 1);
+  constexpr uint32_t idesc = make_idesc(128, D, FMT, 0, 1);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
     if (ks < nks)
-      umma_ts(d_tmem, a_tmem + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes),
-              idesc, (accumulate || ks > 0) ? 1u : 0u);
+      umma_ts(d_tmem, a_tmem + 32 * (ks >> 1) + 8 * (ks & 1), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
+              (accumulate || ks > 0) ? 1u : 0u);
 }
 
 // ------------------------------------------------------------------------------------------------
-// Warps 0-7: row threads, two per query row (thread half h takes keys [64h, 64h+64) of every
-// tile); warp 8: copy producer; warps 9, 10, 11: issuers of S = Q.K^T, of dP = dO.V^T and of
-// dQ += dS.K.  One thread per kind of product: a thread's waits, commits and loop run in sequence
+// Warps 0-15: row threads, four per query row (thread q of a row takes keys [32q, 32q+32) of every
+// tile: sixteen warps keep the schedulers busy while others wait for a product, and the single S buffer of the
+// second sweep is read out in half the time it took with eight); warp 16: copy producer; warps 17, 18, 19:
+// issuers of S = Q.K^T, of dP = dO.V^T and of dQ += dS.K.  One thread per kind of product: a thread's waits, commits and loop run in sequence
 // with its (blocking) issue, and a thread that waits for the operands of one product cannot issue
 // another whose operands are ready (dQ of a tile would wait behind the K tile of the next one,
 // which in turn waits for the ring slot that this very dQ product releases).
 //
 // Tensor-memory columns.  First sweep, tile g in slot j = g & 1: S at 256 j, dP at 256 j + 128.
 // Second sweep: S at 0, dP of tile t at 128 + 128 (t & 1), dQ at 384.  dS overwrites dP as 16-bit
-// pairs: half 0 writes columns [0, 32) of the buffer, half 1 columns [64, 96), each inside the
-// range that the same thread has already read, so the two halves never touch each other's input.
+// pairs: thread q of a row writes columns [32q, 32q+16) of the buffer, inside the range it has already
+// read, so the four never touch each other's input.
 template <int MODE, int D, int FMT, int KIND>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -282,7 +284,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           int nks = 8;
           const int valid = len - (int)sh.tiles[t] * 128;
           if (ok && valid < 128) nks = zero_tail_rows(ring + k_slot(g) * Cfg::kTileBytes, valid, Cfg::kBoxes, 128);
-          if (ok) issue_tn_split<D, FMT>(tmem_acc, tmem + 128 + 128 * bsel, k_addr(g), t > 0, nks);
+          if (ok) issue_tn_quads<D, FMT>(tmem_acc, tmem + 128 + 128 * bsel, k_addr(g), t > 0, nks);
           umma_commit(&sh.dq_done[bsel]);
           umma_commit(&sh.k_empty[k_slot(g)]);
           DQTRACE(true, g, 12);
@@ -293,8 +295,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
     }
     __syncwarp();
   } else {
-    const int half = warp >> 2;
-    const int c0 = half * 64;                 // first key column of this thread inside a tile
+    const int quad = warp >> 2;
+    const int c0 = quad * 32;                 // first key column of this thread inside a tile
     const int row = (warp & 3) * 32 + lane;
     const int i = row0 + row;
     const bool live = i < len;
@@ -322,107 +324,55 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         __syncwarp();
         tc_fence_after_sync();
         const uint32_t t_s = tmem + lane_base + 256 * j + c0, t_dp = t_s + 128;
-        if ((MODE == ENTMAX && KIND == 0 && !need_mask) || (MODE == LAZY && !need_mask && !in_window)) {
-          // Straight-line tiles: the whole half row of S and dP goes to registers first, so that the
-          // slot is handed back before any arithmetic and the products of tile g+2 can follow those
-          // of tile g+1 without a gap.
-          uint32_t r[64], gq[64];
-          tmem_ld32(t_s, r);
-          tmem_ld32(t_s + 32, r + 32);
-          tmem_ld32(t_dp, gq);
-          tmem_ld32(t_dp + 32, gq + 32);
-          tmem_ld_wait_regs32(r);
-          tmem_ld_wait_regs32(r + 32);
-          tmem_ld_wait_regs32(gq);
-          tmem_ld_wait_regs32(gq + 32);
-          tc_fence_before_sync();
-          __syncwarp();
-          float nrs = -rstat;
-          if (lane == 0) {
-            nrs = __uint_as_float(mbar_arrive_token(&sh.t_free[j])) - rstat;   // (token: see mbar_arrive_token)
-            if (g == nact - 1) mbar_arrive(&sh.sweep_done);
-          }
-          DQTRACE(tid == 0, g, 10);
-          if (MODE == ENTMAX) {
-            uint64_t sa = pack2(acc_a0, acc_a1), sb = pack2(acc_b0, acc_b1);
-#pragma unroll
-            for (int x = 0; x < 64; x += 2) {
-              const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, nrs));
-              const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
-              const uint64_t ee = pack2(e0, e1);
-              sa = fma2(ee, pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])), sa);
-              sb = add2(sb, ee);
-            }
-            unpack2(sa, acc_a0, acc_a1);
-            unpack2(sb, acc_b0, acc_b1);
-          } else {
-#pragma unroll
-            for (int x = 0; x < 64; x += 2) {
-              const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, nrs));
-              const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
-              const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
-              const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
-              acc_a0 = fmaf(w0, md0, acc_a0); acc_b0 += md0;
-              acc_a1 = fmaf(w1, md1, acc_a1); acc_b1 += md1;
-            }
-          }
-          continue;
+        // this thread's 32 columns of S and dP go to registers first, so that the slot is handed back
+        // before any arithmetic and the products of tile g+2 can follow those of tile g+1 without a gap
+        uint32_t r[32], gq[32];
+        tmem_ld32(t_s, r);
+        tmem_ld32(t_dp, gq);
+        tmem_ld_wait_regs32(r);
+        tmem_ld_wait_regs32(gq);
+        tc_fence_before_sync();
+        __syncwarp();
+        float nrs = -rstat;
+        if (lane == 0) {
+          nrs = __uint_as_float(mbar_arrive_token(&sh.t_free[j])) - rstat;   // (token: see mbar_arrive_token)
+          if (g == nact - 1) mbar_arrive(&sh.sweep_done);
         }
-        // 32 columns at a time: a small loop body stays inside the instruction cache
-#pragma unroll 1
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t r[32], gq[32];
-          tmem_ld32(t_s + ch * 32, r);
-          tmem_ld32(t_dp + ch * 32, gq);
-          tmem_ld_wait_regs32(r);
-          tmem_ld_wait_regs32(gq);
-          if (ch == 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(&sh.t_free[j]);
-              if (g == nact - 1) mbar_arrive(&sh.sweep_done);
-            }
-            DQTRACE(tid == 0, g, 10);
-          }
-          if (MODE == ENTMAX && KIND == 0 && !need_mask) {
-            // alpha = 1.5, no masked entry: U = max(x, 0) by one saturating fma; packed sums
-            uint64_t sa = pack2(acc_a0, acc_a1), sb = pack2(acc_b0, acc_b1);
+        DQTRACE(tid == 0, g, 10);
+        if (MODE == ENTMAX && KIND == 0 && !need_mask) {
+          // alpha = 1.5, no masked entry: U = max(x, 0) by one saturating fma; packed sums
+          uint64_t sa = pack2(acc_a0, acc_a1), sb = pack2(acc_b0, acc_b1);
 #pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, -rstat));
-              const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, -rstat));
-              const uint64_t ee = pack2(e0, e1);
-              sa = fma2(ee, pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])), sa);
-              sb = add2(sb, ee);
-            }
-            unpack2(sa, acc_a0, acc_a1);
-            unpack2(sb, acc_b0, acc_b1);
-            continue;
+          for (int x = 0; x < 32; x += 2) {
+            const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, nrs));
+            const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
+            const uint64_t ee = pack2(e0, e1);
+            sa = fma2(ee, pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])), sa);
+            sb = add2(sb, ee);
           }
-          if (MODE == LAZY && !need_mask && !in_window) {
-            // interior tile (no masked entry, no bias): straight-line arithmetic, no branches
+          unpack2(sa, acc_a0, acc_a1);
+          unpack2(sb, acc_b0, acc_b1);
+        } else if (MODE == LAZY && !need_mask && !in_window) {
+          // interior tile (no masked entry, no bias): straight-line arithmetic, no branches
 #pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, -rstat));
-              const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, -rstat));
-              const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
-              const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
-              acc_a0 = fmaf(w0, md0, acc_a0); acc_b0 += md0;
-              acc_a1 = fmaf(w1, md1, acc_a1); acc_b1 += md1;
-            }
-            continue;
+          for (int x = 0; x < 32; x += 2) {
+            const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, nrs));
+            const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
+            const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
+            const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
+            acc_a0 = fmaf(w0, md0, acc_a0); acc_b0 += md0;
+            acc_a1 = fmaf(w1, md1, acc_a1); acc_b1 += md1;
           }
+        } else {
 #pragma unroll
           for (int x = 0; x < 32; ++x) {
-            const int c = ch * 32 + x;
             float xs = __uint_as_float(r[x]) * c1;
             if (MODE == LAZY && in_window) {
-              const int dist = i - (kt * 128 + c0 + c);
+              const int dist = i - (kt * 128 + c0 + x);
               if (dist >= 0 && dist < p.window) xs = fmaf(__ldg(p.bias + (int64_t)h * p.bias_stride + dist), kLog2e, xs);
             }
             if (MODE == ENTMAX) xs = fmaf(__uint_as_float(r[x]), c1, -rstat); else xs -= rstat;
-            const bool valid = !need_mask || c <= climit;
+            const bool valid = !need_mask || x <= climit;
             float pv, w;
             bool m;
             prob_terms<MODE, KIND>(xs, e, tau_row, valid, pv, w, m);
@@ -439,33 +389,33 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       }
       DQTRACE(tid == 0, nact - 1, 11);
       if (nact == 0 && lane == 0) mbar_arrive(&sh.sweep_done);
-      // The two threads of a row meet in tensor memory: both own the same lane.  Columns 384..387
+      // The four threads of a row meet in tensor memory: all own the same lane.  Columns 384..391
       // are free from the moment every row thread has read the last first-sweep tile (the first
       // barrier) until the first dQ product, which needs the delta computed here.
       named_bar_sync(1, kBwdRowThreads);
-      tmem_st2(tmem_acc + lane_base + 2 * half, __float_as_uint(acc_a0 + acc_a1), __float_as_uint(acc_b0 + acc_b1));
+      tmem_st2(tmem_acc + lane_base + 2 * quad, __float_as_uint(acc_a0 + acc_a1), __float_as_uint(acc_b0 + acc_b1));
       tmem_st_wait();
       tc_fence_before_sync();
       named_bar_sync(1, kBwdRowThreads);
       tc_fence_after_sync();
       float delta = 0.f;
       {
-        uint32_t both[4];
-        tmem_ld4_sync(tmem_acc + lane_base, both);
-        const float sa = __uint_as_float(both[0]) + __uint_as_float(both[2]);
-        const float sb = __uint_as_float(both[1]) + __uint_as_float(both[3]);
+        uint32_t all4[8];
+        tmem_ld8_sync(tmem_acc + lane_base, all4);
+        const float sa = (__uint_as_float(all4[0]) + __uint_as_float(all4[2])) + (__uint_as_float(all4[4]) + __uint_as_float(all4[6]));
+        const float sb = (__uint_as_float(all4[1]) + __uint_as_float(all4[3])) + (__uint_as_float(all4[5]) + __uint_as_float(all4[7]));
         if (MODE == ENTMAX) {
           delta = (live && sb > 0.f) ? sa / sb : 0.f;
         } else {
           delta = live ? sa : 0.f;
-          if (p.dtau != nullptr && half == 0) {     // dtau_h += sum_i r_i / (i+1)
+          if (p.dtau != nullptr && quad == 0) {     // dtau_h += sum_i r_i / (i+1)
             float contrib = live ? sb / (float)(i + 1) : 0.f;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
             if (lane == 0 && contrib != 0.f) atomicAdd(p.dtau + h, contrib);
           }
         }
-        if (i < L && half == 0) p.delta[bhl + i] = delta;
+        if (i < L && quad == 0) p.delta[bhl + i] = delta;
       }
 
       // ---- second sweep: dS and dQ ------------------------------------------------------------------
@@ -476,122 +426,63 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         const bool in_window = MODE == LAZY && (row0 - kt * 128 - 127 < p.window);
         const uint32_t t_s = tmem + lane_base + c0, t_dp = tmem + lane_base + 128 + 128 * bsel + c0;
         DQTRACE(tid == 0, nact + t, 8);
-        if ((MODE == ENTMAX && KIND == 0 && !need_mask) || (MODE == LAZY && !need_mask && !in_window)) {
-          // Straight-line tiles: S has a single buffer, so its half row goes to registers as soon as
-          // it exists and the buffer is handed back before dP is even waited for; the S product of
-          // the next tile then overlaps the rest of this one.
-          uint32_t r[64], gq[32], pk[16];
-          mbar_wait(&sh.s_full, t & 1, abort_flag, status, 54);
-          __syncwarp();
-          tc_fence_after_sync();
-          tmem_ld32(t_s, r);
-          tmem_ld32(t_s + 32, r + 32);
-          tmem_ld_wait_regs32(r);
-          tmem_ld_wait_regs32(r + 32);
-          tc_fence_before_sync();
-          __syncwarp();
-          float nrs = -rstat;
-          if (lane == 0) nrs = __uint_as_float(mbar_arrive_token(&sh.s_free)) - rstat;
-          mbar_wait(&sh.dp_full[bsel], (t >> 1) & 1, abort_flag, status, 55);
-          DQTRACE(tid == 0, nact + t, 9);
-          __syncwarp();
-          tc_fence_after_sync();
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
-            tmem_ld32_sync(t_dp + ch * 32, gq);
-            if (ch == 1) DQTRACE(tid == 0, nact + t, 10);
-            if (MODE == ENTMAX) {
-              const uint64_t nd = pack2(-delta, -delta);
-#pragma unroll
-              for (int x = 0; x < 32; x += 2) {
-                const float e0 = __saturatef(fmaf(__uint_as_float(r[ch * 32 + x]), c1, nrs));
-                const float e1 = __saturatef(fmaf(__uint_as_float(r[ch * 32 + x + 1]), c1, nrs));
-                float d0, d1;
-                unpack2(mul2(pack2(e0, e1), add2(pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])), nd)), d0, d1);
-                pk[x >> 1] = pack16<FMT>(d0, d1);
-              }
-            } else {
-#pragma unroll
-              for (int x = 0; x < 32; x += 2) {
-                const float w0 = fast_exp2(fmaf(__uint_as_float(r[ch * 32 + x]), c1, nrs));
-                const float w1 = fast_exp2(fmaf(__uint_as_float(r[ch * 32 + x + 1]), c1, nrs));
-                const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
-                const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
-                pk[x >> 1] = pack16<FMT>(w0 * (md0 - delta), w1 * (md1 - delta));
-              }
-            }
-            tmem_st16(t_dp + ch * 16, pk);
-          }
-          tmem_st_wait();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sh.ds_full[bsel]);
-          DQTRACE(tid == 0, nact + t, 11);
-          continue;
-        }
+        // S has a single buffer, so this thread's columns go to registers as soon as they exist and the
+        // buffer is handed back before dP is even waited for; the S product of the next tile then
+        // overlaps the rest of this one.
+        uint32_t r[32], gq[32], pk[16];
         mbar_wait(&sh.s_full, t & 1, abort_flag, status, 54);
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_ld32(t_s, r);
+        tmem_ld_wait_regs32(r);
+        tc_fence_before_sync();
+        __syncwarp();
+        float nrs = -rstat;
+        if (lane == 0) nrs = __uint_as_float(mbar_arrive_token(&sh.s_free)) - rstat;
         mbar_wait(&sh.dp_full[bsel], (t >> 1) & 1, abort_flag, status, 55);
         DQTRACE(tid == 0, nact + t, 9);
         __syncwarp();
         tc_fence_after_sync();
-        // 32 columns at a time; dS chunk c goes to columns [16c, 16c+16) of this thread's half of
-        // the dP buffer, which an earlier (or this) chunk has already read
-#pragma unroll 1
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t r[32], gq[32], pk[16];
-          tmem_ld32(t_s + ch * 32, r);
-          tmem_ld32(t_dp + ch * 32, gq);
-          tmem_ld_wait_regs32(r);
-          tmem_ld_wait_regs32(gq);
-          if (ch == 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.s_free);
-            DQTRACE(tid == 0, nact + t, 10);
-          }
-          if (MODE == ENTMAX && KIND == 0 && !need_mask) {
-            const uint64_t nd = pack2(-delta, -delta);
+        tmem_ld32_sync(t_dp, gq);
+        DQTRACE(tid == 0, nact + t, 10);
+        if (MODE == ENTMAX && KIND == 0 && !need_mask) {
+          const uint64_t nd = pack2(-delta, -delta);
 #pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, -rstat));
-              const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, -rstat));
-              float d0, d1;
-              unpack2(mul2(pack2(e0, e1), add2(pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])), nd)), d0, d1);
-              pk[x >> 1] = pack16<FMT>(d0, d1);
-            }
-            tmem_st16(t_dp + ch * 16, pk);
-            continue;
+          for (int x = 0; x < 32; x += 2) {
+            const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, nrs));
+            const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
+            float d0, d1;
+            unpack2(mul2(pack2(e0, e1), add2(pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])), nd)), d0, d1);
+            pk[x >> 1] = pack16<FMT>(d0, d1);
           }
-          if (MODE == LAZY && !need_mask && !in_window) {
-            // interior tile: no masked entry, no bias and hence no dbias contribution
+        } else if (MODE == LAZY && !need_mask && !in_window) {
+          // interior tile: no masked entry, no bias and hence no dbias contribution
 #pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, -rstat));
-              const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, -rstat));
-              const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
-              const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
-              pk[x >> 1] = pack16<FMT>(w0 * (md0 - delta), w1 * (md1 - delta));
-            }
-            tmem_st16(t_dp + ch * 16, pk);
-            continue;
+          for (int x = 0; x < 32; x += 2) {
+            const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, nrs));
+            const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
+            const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
+            const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
+            pk[x >> 1] = pack16<FMT>(w0 * (md0 - delta), w1 * (md1 - delta));
           }
+        } else {
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
             float dsv[2];
 #pragma unroll
             for (int y = 0; y < 2; ++y) {
-              const int c = ch * 32 + x + y;
-              float xs = __uint_as_float(r[x + y]) * c1;
+              const int c = x + y;
+              float xs = __uint_as_float(r[c]) * c1;
               if (MODE == LAZY && in_window) {
                 const int dist = i - (kt * 128 + c0 + c);
                 if (dist >= 0 && dist < p.window) xs = fmaf(__ldg(p.bias + (int64_t)h * p.bias_stride + dist), kLog2e, xs);
               }
-              if (MODE == ENTMAX) xs = fmaf(__uint_as_float(r[x + y]), c1, -rstat); else xs -= rstat;
+              if (MODE == ENTMAX) xs = fmaf(__uint_as_float(r[c]), c1, -rstat); else xs -= rstat;
               const bool valid = !need_mask || c <= climit;
               float pv, w;
               bool m;
               prob_terms<MODE, KIND>(xs, e, tau_row, valid, pv, w, m);
-              const float dp = __uint_as_float(gq[x + y]);
+              const float dp = __uint_as_float(gq[c]);
               // masked entries: exactly zero, whatever dP holds there (padding may be NaN)
               const float ds = MODE == ENTMAX ? (m ? w * (dp - delta) : 0.f) : (valid ? w * ((m ? dp : 0.f) - delta) : 0.f);
               dsv[y] = ds;
@@ -605,8 +496,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             }
             pk[x >> 1] = pack16<FMT>(dsv[0], dsv[1]);
           }
-          tmem_st16(t_dp + ch * 16, pk);
         }
+        tmem_st16(t_dp, pk);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
@@ -616,21 +507,20 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       mbar_wait(&sh.acc_full, 0, abort_flag, status, 56);   // (committed even when no tile was visited)
       __syncwarp();
       tc_fence_after_sync();
-      // each of the two threads of a row stores half of the dQ columns
-#pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int ch = half * (D / 64) + cc;
+      // each of the four threads of a row stores a quarter of the dQ columns
+      {
         uint32_t r[32];
-        tmem_ld32_sync(tmem_acc + lane_base + ch * 32, r);
+        if (D == 128) tmem_ld32_sync(tmem_acc + lane_base + quad * 32, r);
+        else { tmem_ld16(tmem_acc + lane_base + quad * 16, r); tmem_ld_wait_regs16(r); }
         if (i < L) {
 #pragma unroll
-          for (int x = 0; x < 32; x += 8) {
+          for (int x = 0; x < D / 4; x += 8) {
             uint4 w;
             w.x = (live && nact > 0) ? pack16<FMT>(__uint_as_float(r[x + 0]) * p.scale, __uint_as_float(r[x + 1]) * p.scale) : 0u;
             w.y = (live && nact > 0) ? pack16<FMT>(__uint_as_float(r[x + 2]) * p.scale, __uint_as_float(r[x + 3]) * p.scale) : 0u;
             w.z = (live && nact > 0) ? pack16<FMT>(__uint_as_float(r[x + 4]) * p.scale, __uint_as_float(r[x + 5]) * p.scale) : 0u;
             w.w = (live && nact > 0) ? pack16<FMT>(__uint_as_float(r[x + 6]) * p.scale, __uint_as_float(r[x + 7]) * p.scale) : 0u;
-            *(uint4*)(grow + (ch * 32 + x) * 2) = w;
+            *(uint4*)(grow + (quad * (D / 4) + x) * 2) = w;
           }
         }
       }
@@ -644,7 +534,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       }
     } else if (i < L) {
 #pragma unroll
-      for (int x = 0; x < D / 2; x += 8) *(uint4*)(grow + (half * (D / 2) + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
+      for (int x = 0; x < D / 4; x += 8) *(uint4*)(grow + (quad * (D / 4) + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
     }
     tc_fence_before_sync();
   }

@@ -51,21 +51,6 @@ struct KvShared {
   uint16_t tiles[kKvMaxTiles];    // query tile (128-row units) in the low 9 bits, head of the group above
 };
 
-// D[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory as four pieces of 16 columns (16-bit
-// pairs), piece q at a_tmem + 32 q (each of the four threads of a key row writes its 32 queries inside the
-// columns it read); B a [128 rows x D] tile whose rows are the reduction dimension.  `nks`: 16-row steps
-// to issue (fewer for the tile that reaches into a sequence's padding).
-template <int D, int FMT>
-__device__ __forceinline__ void issue_tn_quads(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
-                                               int nks = 8) {
-  constexpr uint32_t idesc = make_idesc(128, D, FMT, 0, 1);
-#pragma unroll
-  for (int ks = 0; ks < 8; ++ks)
-    if (ks < nks)
-      umma_ts(d_tmem, a_tmem + 32 * (ks >> 1) + 8 * (ks & 1), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
-              (accumulate || ks > 0) ? 1u : 0u);
-}
-
 template <int MODE, int D, int FMT, int KIND>
 __global__ void __launch_bounds__(kKvThreads, 1)
 dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
