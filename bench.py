@@ -476,6 +476,8 @@ def main():
     reps = max(3, min(args.steps, 10))
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(reps)]
     per_kernel = {"fwd": [], "dq": [], "dkdv": []}
+    cta_ms = {"fwd": [], "dq": [], "dkdv": []}
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
     torch.cuda.synchronize()
     for ev in marks:
         q.grad = k.grad = v.grad = None
@@ -486,9 +488,11 @@ def main():
         out.backward(do)
         ev[2].record()
         torch.cuda.synchronize()
-        for name, val in fla.read_status(dev)["kernel_ms"].items():
+        st_now = fla.read_status(dev)
+        for name, val in st_now["kernel_ms"].items():
             if val is not None:
                 per_kernel[name].append(val)
+                cta_ms[name].append(st_now["cta_ms"][name])
     fwd_ms = sum(ev[0].elapsed_time(ev[1]) for ev in marks) / reps
     bwd_ms = sum(ev[1].elapsed_time(ev[2]) for ev in marks) / reps
     peak, peak_sustained, peak_kind = measured_peaks()
@@ -511,8 +515,11 @@ def main():
             continue
         kms = statistics.median(vals)
         ktf = credit[name] * unit / (kms * 1e-3) / 1e12
+        # share of the launch during which the SMs held a CTA of the kernel (one CTA per SM): what is missing
+        # from 1 is dispatch gaps between CTAs plus the tail of the grid, the most a persistent scheduler could win
+        busy = statistics.median(c / (n_sm * m) for c, m in zip(cta_ms[name], vals))
         kernels[name] = {"what": labels[name], "ms": kms, "credited_units": credit[name], "tflops": ktf,
-                         "frac": ktf / peak_sustained}
+                         "frac": ktf / peak_sustained, "sm_occupied_frac": busy}
         # DRAM bytes per launch: an ncu capture of a smaller workload of the same kernel, scaled by the number of
         # (batch, head, row) units (the (batch, head)-major grid keeps shared tiles in L2, so traffic follows the
         # tensor sizes); entmax kernels at D = 128 without varlen only

@@ -104,13 +104,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Kernel clocks for the caller's status words (fla_attn_geom.status, int32[32], 8-byte aligned): kernel
 // `which` (0 forward, 1 dQ, 2 dK/dV) keeps the earliest start and the latest end of its CTAs, in
 // nanoseconds of the GPU's global timer, at 64-bit words 4 + 2 which (bitwise complement of the start,
-// so that the zero the caller clears the words to means "not set") and 5 + 2 which.
+// so that the zero the caller clears the words to means "not set") and 5 + 2 which, and adds every CTA's
+// lifetime (start to end) to 64-bit word 13 + which: lifetimes / (SMs x span) is the share of the launch
+// during which an SM held a CTA of this kernel (one CTA per SM), i.e. what dispatch gaps and the tail of
+// the grid leave on the table.  Called by thread 0 of the CTA, once with end = false and once with true.
 __device__ __forceinline__ void kernel_clock(int* status, int which, bool end) {
+  __shared__ unsigned long long cta_start;
   if (status == nullptr) return;
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   unsigned long long* w = reinterpret_cast<unsigned long long*>(status + 8) + 2 * which;
-  if (end) atomicMax(w + 1, t); else atomicMax(w, ~t);
+  if (end) {
+    atomicMax(w + 1, t);
+    atomicAdd(reinterpret_cast<unsigned long long*>(status + 26) + which, t - cta_start);
+  } else {
+    cta_start = t;
+    atomicMax(w, ~t);
+  }
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

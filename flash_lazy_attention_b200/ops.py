@@ -88,8 +88,10 @@ def _status_buf(device: torch.device) -> torch.Tensor:
 
 def read_status(device=None, reset: bool = False) -> dict:
     """Synchronising read of the device status words: {"error", "wait_tag", "block", "tile_mmas",
-    "list_ctas", "pass_ctas", "kernel_ms"}.
-    ``tile_mmas`` counts 128x128xD tile products issued by tensor-core kernels since the last reset."""
+    "list_ctas", "pass_ctas", "kernel_ms", "cta_ms"}.
+    ``tile_mmas`` counts 128x128xD tile products issued by tensor-core kernels since the last reset;
+    ``cta_ms`` is the sum of the lifetimes of a kernel's CTAs (one CTA per SM: divided by SMs x kernel_ms it
+    is the share of the launch during which the SMs were occupied)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     buf = _status_buf(device)
     vals = buf.cpu().tolist()
@@ -97,7 +99,9 @@ def read_status(device=None, reset: bool = False) -> dict:
         buf.zero_()
     return {"error": vals[0], "wait_tag": vals[1], "block": vals[2],
             "tile_mmas": (vals[4] & 0xFFFFFFFF) | ((vals[5] & 0xFFFFFFFF) << 32),
-            "list_ctas": vals[6], "pass_ctas": vals[7], "kernel_ms": _kernel_ms(vals)}
+            "list_ctas": vals[6], "pass_ctas": vals[7], "kernel_ms": _kernel_ms(vals),
+            "cta_ms": {name: ((vals[26 + 2 * i] & 0xFFFFFFFF) | ((vals[27 + 2 * i] & 0xFFFFFFFF) << 32)) * 1e-6
+                       for i, name in enumerate(("fwd", "dq", "dkdv"))}}
 
 
 def _kernel_ms(vals) -> dict:

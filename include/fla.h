@@ -76,8 +76,11 @@ typedef struct fla_attn_geom {
                            * over score tiles; [8..19]: as 64-bit words, per kernel (forward, dQ,  *
                            * dK/dV) the bitwise complement of the earliest start and the latest   *
                            * end of its CTAs in nanoseconds of the GPU's global timer (0 = not    *
-                           * set): the live per-kernel durations of the benchmark.  Never cleared  *
-                           * by the library; the caller zeroes it.                                */
+                           * set): the live per-kernel durations of the benchmark; [26..31]: as   *
+                           * 64-bit words, per kernel the sum of its CTAs' lifetimes in the same   *
+                           * nanoseconds (divided by SMs x duration: the share of the launch the   *
+                           * SMs were occupied).  Never cleared by the library; the caller zeroes  *
+                           * it.                                                                   */
   int32_t flags;          /* FLA_FLAG_*                                                         */
   int32_t Hkv;            /* grouped-query attention: k, v, dk, dv are [B,Hkv,L,D] views and query  *
                            * head h uses head h / (H / Hkv) of them; 0 or H: every query head its  *
