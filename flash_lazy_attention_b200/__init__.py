@@ -3,6 +3,7 @@ from .ops import (adasplash, adasplash_no_block_mask, check_status, entmax_atten
                   last_call_info, lazy_attention_triton, read_status, set_flags, set_path, triton_entmax,
                   unpack_block_mask)
 
+from . import custom_ops  # noqa: F401,E402  (registers torch.ops.flash_lazy.*)
 from .layers import LazyAttention, LazyAttentionLayer  # noqa: F401,E402
 
 __all__ = ["LazyAttention", "LazyAttentionLayer", "adasplash", "adasplash_no_block_mask", "triton_entmax", "lazy_attention_triton",

@@ -212,25 +212,36 @@ class EntmaxAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
-        lib = _lib.load()
         q, k, v, tau, aux_o, aux_s, mask, vl = ctx.saved_tensors
-        do = _tma_friendly(do)
-        with torch.cuda.device(q.device):
-            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-            dk, dv = (torch.empty(k.shape, dtype=q.dtype, device=q.device) for _ in range(2))
-            g = _geom(q, ctx.is_causal, vl, ctx.kv_heads)
-            nbytes = lib.fla_entmax_attn_bwd_workspace(g)
-            ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
-            rc = lib.fla_entmax_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(do), ctx.alpha, tau.data_ptr(),
-                                         aux_o.data_ptr() if aux_o is not None else None,
-                                         aux_s.data_ptr() if aux_s is not None else None,
-                                         mask.data_ptr() if mask is not None else None,
-                                         _t4(dq), _t4(dk), _t4(dv), ws.data_ptr(), nbytes, _stream(q))
-            _lib.check(rc, "fla_entmax_attn_bwd")
+        dq, dk, dv = entmax_attention_backward(q, k, v, do, tau, aux_o, aux_s, mask, vl, ctx.alpha, ctx.is_causal,
+                                               ctx.kv_heads)
         return dq, dk, dv, None, None, None, None, None, None
 
 
+def entmax_attention_backward(q, k, v, do, tau, aux_o, aux_s, mask, vl, alpha, is_causal, kv_heads=0):
+    """(dq, dk, dv) from the forward's saved state (tau; aux_o, aux_s on the SIMT family; the block mask or None);
+    ``vl``: int32 lengths on q's device or None."""
+    lib = _lib.load()
+    do = _tma_friendly(do)
+    with torch.cuda.device(q.device):
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk, dv = (torch.empty(k.shape, dtype=q.dtype, device=q.device) for _ in range(2))
+        g = _geom(q, is_causal, vl, kv_heads)
+        nbytes = lib.fla_entmax_attn_bwd_workspace(g)
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+        rc = lib.fla_entmax_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(do), float(alpha), tau.data_ptr(),
+                                     aux_o.data_ptr() if aux_o is not None else None,
+                                     aux_s.data_ptr() if aux_s is not None else None,
+                                     mask.data_ptr() if mask is not None else None,
+                                     _t4(dq), _t4(dk), _t4(dv), ws.data_ptr(), nbytes, _stream(q))
+        _lib.check(rc, "fla_entmax_attn_bwd")
+    return dq, dk, dv
+
+
 def _entmax_attn(q, k, v, alpha, niter, is_causal, varlen, use_block_mask):
+    if torch.compiler.is_compiling():   # one opaque node in the traced graph (custom_ops.py)
+        return torch.ops.flash_lazy.entmax_attn_fwd(q, k, v, float(alpha), int(niter), bool(is_causal), varlen,
+                                                    bool(use_block_mask))[0]
     if k.dim() == 4 and q.dim() == 4 and k.shape[1] != q.shape[1] and q.is_cuda:
         q_, k_, v_ = _qkv_checked(q, k, v)
         k, v, kvh = _shared_kv(_lib.load(), q_, k_, v_, is_causal, _varlen32(varlen, q_))
@@ -250,7 +261,7 @@ def adasplash_no_block_mask(q, k, v, alpha=1.5, niter=10, is_causal=False, varle
 
 
 def entmax_attention_forward(q, k, v, alpha=1.5, niter=10, is_causal=False, varlen=None,
-                             use_block_mask=True, need_aux=False):
+                             use_block_mask=True, need_aux=False, kv_heads=0):
     """Forward only, returning every side product: (out, tau, aux_o, aux_s, block_mask).
     The threshold rows ``tau`` are in (alpha-1)*score units; ``block_mask`` is an int32
     [B,H,ceil(L/128),words] bit array, bit J of a row = key block J (64 keys) is non-zero."""
@@ -267,7 +278,7 @@ def entmax_attention_forward(q, k, v, alpha=1.5, niter=10, is_causal=False, varl
         if use_block_mask:
             mask = torch.empty((B, H, (L + 127) // 128, lib.fla_block_mask_words(L)), dtype=torch.int32,
                                device=q.device)
-        g = _geom(q, is_causal, vl)
+        g = _geom(q, is_causal, vl, kv_heads)
         rc = lib.fla_entmax_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), float(alpha),
                                      int(niter), tau.data_ptr(), aux_o.data_ptr() if need_aux else None,
                                      aux_s.data_ptr() if need_aux else None,
@@ -287,60 +298,84 @@ def unpack_block_mask(mask: torch.Tensor, L: int) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 # Lazy Attention
 # ---------------------------------------------------------------------------------------------
+def lazy_attention_forward(q, k, v, bias, tau, window, varlen=None, need_aux=False, kv_heads=0):
+    """Forward only: (out, lse, aux_o).  ``lse`` is the base-2 log-sum-exp of the rows (saved state of the backward);
+    ``aux_o`` (fp32 [B,H,L,2D]) is what the SIMT family's backward needs, None unless asked for."""
+    lib = _lib.load()
+    q, k, v = _qkv_checked(q, k, v)
+    B, H, L, D = q.shape
+    if bias.dim() != 2 or bias.shape[0] != H or tau.numel() != H:
+        raise ValueError("bias must be [H, W] and tau [H]")
+    window = int(window)
+    if window > bias.shape[1]:
+        raise ValueError(f"window_size {window} exceeds the {bias.shape[1]} bias columns")
+    vl = _varlen32(varlen, q)
+    bias32 = bias.detach().to(device=q.device, dtype=torch.float32).contiguous()
+    tau32 = tau.detach().to(device=q.device, dtype=torch.float32).contiguous().view(-1)
+    with torch.cuda.device(q.device):
+        g = _geom(q, True, vl, kv_heads)
+        out = torch.empty((B, H, L, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, L), dtype=torch.float32, device=q.device)
+        aux_o = torch.empty((B, H, L, 2 * D), dtype=torch.float32, device=q.device) if need_aux else None
+        rc = lib.fla_lazy_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), bias32.data_ptr(),
+                                   bias32.stride(0), tau32.data_ptr(), window, lse.data_ptr(),
+                                   aux_o.data_ptr() if need_aux else None, _stream(q))
+        _lib.check(rc, "fla_lazy_attn_fwd")
+    return out, lse, aux_o
+
+
+def lazy_attention_backward(q, k, v, out, do, bias, tau, window, lse, aux_o, vl, want_params, kv_heads=0):
+    """(dq, dk, dv, dbias, dtau); dbias [H, bias columns] and dtau [H] are fp32 like the reference's
+    (lazy_attention_triton.py:532-533) and None unless ``want_params``."""
+    lib = _lib.load()
+    do = _tma_friendly(do)
+    H = q.shape[1]
+    bias32 = bias.detach().to(device=q.device, dtype=torch.float32).contiguous()
+    tau32 = tau.detach().to(device=q.device, dtype=torch.float32).contiguous().view(-1)
+    with torch.cuda.device(q.device):
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk, dv = (torch.empty(k.shape, dtype=q.dtype, device=q.device) for _ in range(2))
+        dbias = dtau = None
+        if want_params:
+            dbias = torch.zeros(tuple(bias.shape), dtype=torch.float32, device=q.device)
+            dtau = torch.zeros((H,), dtype=torch.float32, device=q.device)
+        g = _geom(q, True, vl, kv_heads)
+        nbytes = lib.fla_lazy_attn_bwd_workspace(g)
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+        rc = lib.fla_lazy_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(out), _t4(do), bias32.data_ptr(),
+                                   bias32.stride(0), tau32.data_ptr(), int(window), lse.data_ptr(),
+                                   aux_o.data_ptr() if aux_o is not None else None, _t4(dq), _t4(dk), _t4(dv),
+                                   dbias.data_ptr() if want_params else None,
+                                   dbias.stride(0) if want_params else 0,
+                                   dtau.data_ptr() if want_params else None,
+                                   ws.data_ptr(), nbytes, _stream(q))
+        _lib.check(rc, "fla_lazy_attn_bwd")
+    return dq, dk, dv, dbias, dtau
+
+
 class LazyAttentionFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, bias, tau, window_size, varlen=None, kv_heads=0):
         lib = _lib.load()
         q, k, v = _qkv_checked(q, k, v)
-        B, H, L, D = q.shape
-        if bias.dim() != 2 or bias.shape[0] != H or tau.numel() != H:
-            raise ValueError("bias must be [H, W] and tau [H]")
-        window = int(window_size)
-        if window > bias.shape[1]:
-            raise ValueError(f"window_size {window} exceeds the {bias.shape[1]} bias columns")
         vl = _varlen32(varlen, q)
-        bias32 = bias.detach().to(device=q.device, dtype=torch.float32).contiguous()
-        tau32 = tau.detach().to(device=q.device, dtype=torch.float32).contiguous().view(-1)
         with torch.cuda.device(q.device):
             g = _geom(q, True, vl, kv_heads)
             need_aux = any(ctx.needs_input_grad[:5]) and not lib.fla_attn_uses_tensor_cores(g, _t4(q), _t4(k), _t4(v))
-            out = torch.empty((B, H, L, D), dtype=q.dtype, device=q.device)
-            lse = torch.empty((B, H, L), dtype=torch.float32, device=q.device)
-            aux_o = torch.empty((B, H, L, 2 * D), dtype=torch.float32, device=q.device) if need_aux else None
-            rc = lib.fla_lazy_attn_fwd(g, _t4(q), _t4(k), _t4(v), _t4(out), bias32.data_ptr(),
-                                       bias32.stride(0), tau32.data_ptr(), window, lse.data_ptr(),
-                                       aux_o.data_ptr() if need_aux else None, _stream(q))
-            _lib.check(rc, "fla_lazy_attn_fwd")
+        out, lse, aux_o = lazy_attention_forward(q, k, v, bias, tau, window_size, vl, need_aux, kv_heads)
+        bias32 = bias.detach().to(device=q.device, dtype=torch.float32).contiguous()
+        tau32 = tau.detach().to(device=q.device, dtype=torch.float32).contiguous().view(-1)
         ctx.save_for_backward(q, k, v, out, bias32, tau32, lse, aux_o, vl)
-        ctx.window, ctx.kv_heads = window, int(kv_heads)
+        ctx.window, ctx.kv_heads = int(window_size), int(kv_heads)
         ctx.bias_shape, ctx.tau_shape = tuple(bias.shape), tuple(tau.shape)
         return out
 
     @staticmethod
     def backward(ctx, do):
-        lib = _lib.load()
         q, k, v, out, bias32, tau32, lse, aux_o, vl = ctx.saved_tensors
-        do = _tma_friendly(do)
-        H = q.shape[1]
         want_params = ctx.needs_input_grad[3] or ctx.needs_input_grad[4]
-        with torch.cuda.device(q.device):
-            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-            dk, dv = (torch.empty(k.shape, dtype=q.dtype, device=q.device) for _ in range(2))
-            dbias = dtau = None
-            if want_params:  # fp32 like the reference (lazy_attention_triton.py:532-533)
-                dbias = torch.zeros(ctx.bias_shape, dtype=torch.float32, device=q.device)
-                dtau = torch.zeros((H,), dtype=torch.float32, device=q.device)
-            g = _geom(q, True, vl, ctx.kv_heads)
-            nbytes = lib.fla_lazy_attn_bwd_workspace(g)
-            ws = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
-            rc = lib.fla_lazy_attn_bwd(g, _t4(q), _t4(k), _t4(v), _t4(out), _t4(do), bias32.data_ptr(),
-                                       bias32.stride(0), tau32.data_ptr(), ctx.window, lse.data_ptr(),
-                                       aux_o.data_ptr() if aux_o is not None else None, _t4(dq), _t4(dk), _t4(dv),
-                                       dbias.data_ptr() if want_params else None,
-                                       dbias.stride(0) if want_params else 0,
-                                       dtau.data_ptr() if want_params else None,
-                                       ws.data_ptr(), nbytes, _stream(q))
-            _lib.check(rc, "fla_lazy_attn_bwd")
+        dq, dk, dv, dbias, dtau = lazy_attention_backward(q, k, v, out, do, bias32, tau32, ctx.window, lse, aux_o, vl,
+                                                          want_params, ctx.kv_heads)
         if want_params:
             dtau = dtau.view(ctx.tau_shape)
         return dq, dk, dv, dbias, dtau, None, None, None
@@ -352,6 +387,8 @@ def lazy_attention_triton(q, k, v, bias, tau, window_size=None, varlen=None):
     heads than q (grouped-query attention: Hkv dividing H); bias and tau are per query head."""
     if window_size is None:
         window_size = bias.shape[1]
+    if torch.compiler.is_compiling():   # one opaque node in the traced graph (custom_ops.py)
+        return torch.ops.flash_lazy.lazy_attn_fwd(q, k, v, bias, tau, int(window_size), varlen)[0]
     kvh = 0
     if k.dim() == 4 and q.dim() == 4 and k.shape[1] != q.shape[1] and q.is_cuda:
         q_, k_, v_ = _qkv_checked(q, k, v)
@@ -362,46 +399,57 @@ def lazy_attention_triton(q, k, v, bias, tau, window_size=None, varlen=None):
 # ---------------------------------------------------------------------------------------------
 # stand-alone entmax
 # ---------------------------------------------------------------------------------------------
+def entmax_rows_forward(x, alpha, n_iter, fast_math):
+    """y = entmax(x) over the last dimension, in x's dtype (float64 is computed in float32 and returned so)."""
+    lib = _lib.load()
+    if not x.is_cuda:
+        raise RuntimeError("x must be a CUDA tensor: this library has no CPU path")
+    xc = x.contiguous()
+    if xc.dtype == torch.float64:
+        xc = xc.float()
+    if xc.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {x.dtype}")
+    cols = xc.shape[-1] if xc.dim() > 0 else 1
+    rows = xc.numel() // max(cols, 1)
+    with torch.cuda.device(x.device):
+        y = torch.empty_like(xc)
+        rc = lib.fla_entmax_fwd(xc.data_ptr(), y.data_ptr(), rows, cols, float(alpha), int(n_iter),
+                                int(bool(fast_math)), _DTYPES[xc.dtype], _stream(x))
+        _lib.check(rc, "fla_entmax_fwd")
+    return y
+
+
+def entmax_rows_backward(y, dy, alpha):
+    lib = _lib.load()
+    dyc = dy.contiguous().to(y.dtype)
+    cols = y.shape[-1] if y.dim() > 0 else 1
+    rows = y.numel() // max(cols, 1)
+    with torch.cuda.device(y.device):
+        dx = torch.empty_like(y)
+        rc = lib.fla_entmax_bwd(y.data_ptr(), dyc.data_ptr(), dx.data_ptr(), rows, cols, float(alpha),
+                                _DTYPES[y.dtype], _stream(y))
+        _lib.check(rc, "fla_entmax_bwd")
+    return dx
+
+
 class EntmaxFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, alpha, n_iter, fast_math):
-        lib = _lib.load()
-        if not x.is_cuda:
-            raise RuntimeError("x must be a CUDA tensor: this library has no CPU path")
-        orig_dtype = x.dtype
-        xc = x.contiguous()
-        if orig_dtype == torch.float64:
-            xc = xc.float()
-        if xc.dtype not in _DTYPES:
-            raise TypeError(f"unsupported dtype {orig_dtype}")
-        cols = xc.shape[-1] if xc.dim() > 0 else 1
-        rows = xc.numel() // max(cols, 1)
-        with torch.cuda.device(x.device):
-            y = torch.empty_like(xc)
-            rc = lib.fla_entmax_fwd(xc.data_ptr(), y.data_ptr(), rows, cols, float(alpha), int(n_iter),
-                                    int(bool(fast_math)), _DTYPES[xc.dtype], _stream(x))
-            _lib.check(rc, "fla_entmax_fwd")
+        y = entmax_rows_forward(x, alpha, n_iter, fast_math)
         ctx.save_for_backward(y)
-        ctx.alpha, ctx.orig_dtype = float(alpha), orig_dtype
-        return y.to(orig_dtype) if orig_dtype == torch.float64 else y
+        ctx.alpha, ctx.orig_dtype = float(alpha), x.dtype
+        return y.to(x.dtype) if x.dtype == torch.float64 else y
 
     @staticmethod
     def backward(ctx, dy):
-        lib = _lib.load()
         (y,) = ctx.saved_tensors
-        dyc = dy.contiguous().to(y.dtype)
-        cols = y.shape[-1] if y.dim() > 0 else 1
-        rows = y.numel() // max(cols, 1)
-        with torch.cuda.device(y.device):
-            dx = torch.empty_like(y)
-            rc = lib.fla_entmax_bwd(y.data_ptr(), dyc.data_ptr(), dx.data_ptr(), rows, cols, ctx.alpha,
-                                    _DTYPES[y.dtype], _stream(y))
-            _lib.check(rc, "fla_entmax_bwd")
-        return dx.to(ctx.orig_dtype), None, None, None
+        return entmax_rows_backward(y, dy, ctx.alpha).to(ctx.orig_dtype), None, None, None
 
 
 def triton_entmax(x, alpha=1.5, n_iter=10, fast_math=True):
     """alpha-entmax over the last dimension (Halley/Newton on the threshold, bisection-safeguarded)."""
+    if torch.compiler.is_compiling():   # one opaque node in the traced graph (custom_ops.py)
+        return torch.ops.flash_lazy.entmax_rows_fwd(x, float(alpha), int(n_iter), bool(fast_math)).to(x.dtype)
     return EntmaxFunc.apply(x, alpha, n_iter, fast_math)
 
 
