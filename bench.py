@@ -200,6 +200,15 @@ def rows_table(steps, warmup):
                               "bwd_ms": round(ms_b, 4), "bwd_gbs": round(3 * nb / ms_b / 1e6, 1),
                               "peak_gbs": peak}), flush=True)
             del x, dy, y
+    # rotary embedding of q and k in one launch (the step before attention in the layers): read + write of both
+    for B, L, H, Hk, D in ((8, 8192, 32, 32, 128), (4, 16384, 32, 8, 128), (8, 4096, 16, 16, 64)):
+        q = torch.randn(B, L, H, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)    # b l h d storage
+        k = torch.randn(B, L, Hk, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+        ms = timed(lambda: fla.rope_qk(q, k, 10000.0, 0))
+        nb = 2 * (q.numel() + k.numel()) * q.element_size()
+        print(json.dumps({"op": "rope_qk", "dtype": "bf16", "B": B, "L": L, "H": H, "Hkv": Hk, "D": D,
+                          "ms": round(ms, 4), "gbs": round(nb / ms / 1e6, 1), "peak_gbs": peak}), flush=True)
+        del q, k
 
 
 def lazy_compare(steps, warmup):

@@ -41,6 +41,8 @@ SIGNATURES = {
     "fla_attn_uses_tensor_cores": (C.c_int, [_PG, _P4, _P4, _P4]),
     "fla_entmax_fwd": (C.c_int, [_vp, _vp, _i64, _i64, _f32, C.c_int, C.c_int, C.c_int, _vp]),
     "fla_entmax_bwd": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _f32, C.c_int, _vp]),
+    "fla_rope_qk": (C.c_int, [_P4, _P4, C.c_int32, _P4, _P4, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _f32,
+                              C.c_int32, C.c_int32, _vp]),
     "fla_block_mask_words": (_i64, [_i32]),
     "fla_check_status": (C.c_int, [_vp, _vp]),
     "fla_entmax_attn_fwd": (C.c_int, [_PG, _P4, _P4, _P4, _P4, _f32, C.c_int, _vp, _vp, _vp, _vp, _vp]),

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libflashlazy.so")
-SOURCES = ["fla_api.cu", "simt_attn.cu", "entmax_rows.cu", "tc_selftest.cu", "tc_attn.cu"]
+SOURCES = ["fla_api.cu", "simt_attn.cu", "entmax_rows.cu", "rope.cu", "tc_selftest.cu", "tc_attn.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

@@ -21,6 +21,8 @@ cudaError_t simt_attn_bwd(int mode, const AttnParams& p, int dtype, cudaStream_t
 cudaError_t attn_delta(int mode, const AttnParams& p, int dtype, cudaStream_t st);
 cudaError_t entmax_rows_fwd(const void* x, void* y, int64_t rows, int64_t cols, float alpha, int n_iter, int fast,
                             int dtype, cudaStream_t st);
+cudaError_t rope_qk_launch(const View4* in, const View4* out, const int* heads, int B, int L, int D, float base,
+                           int offset, int inverse, int dtype, cudaStream_t st);
 cudaError_t entmax_rows_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t cols, float alpha,
                             int dtype, cudaStream_t st);
 cudaError_t selftest_umma_launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const void* a, float* c,
@@ -226,6 +228,30 @@ int fla_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_
   if (rows == 0) return FLA_OK;
   cudaError_t e = entmax_rows_bwd(y, dy, dx, rows, cols, alpha, dtype, (cudaStream_t)stream);
   return e == cudaSuccess ? FLA_OK : cuda_fail(e, "entmax backward launch");
+}
+
+int fla_rope_qk(const fla_tensor4* q_in, const fla_tensor4* q_out, int32_t Hq, const fla_tensor4* k_in,
+                const fla_tensor4* k_out, int32_t Hk, int32_t B, int32_t L, int32_t D, int32_t dtype, float base,
+                int32_t offset, int32_t inverse, void* stream) {
+  if (!q_in || !q_out || !q_in->ptr || !q_out->ptr) return fail(FLA_ERR_INVALID, "q_in or q_out is NULL");
+  if ((k_in == nullptr) != (k_out == nullptr)) return fail(FLA_ERR_INVALID, "k_in and k_out must both be given or both be NULL");
+  if (dtype < FLA_F32 || dtype > FLA_BF16) return fail(FLA_ERR_INVALID, "unknown dtype %d", dtype);
+  if (B < 0 || L < 0 || Hq < 1 || (k_in && Hk < 1)) return fail(FLA_ERR_INVALID, "bad shape B=%d L=%d Hq=%d Hk=%d", B, L, Hq, Hk);
+  if (D < 2 || D % 2 != 0) return fail(FLA_ERR_INVALID, "head dim %d: rotate-half needs an even head dimension", D);
+  if (!(base > 0.f)) return fail(FLA_ERR_INVALID, "base must be positive");
+  View4 in[2] = {}, out[2] = {};
+  const fla_tensor4* src[4] = {q_in, q_out, k_in, k_out};
+  for (int t = 0; t < 4; ++t) {
+    if (!src[t]) continue;
+    if (!src[t]->ptr) return fail(FLA_ERR_INVALID, "a tensor pointer is NULL");
+    if (src[t]->stride[3] != 1) return fail(FLA_ERR_UNSUPPORTED, "the head dimension must have stride 1");
+    View4& v = (t & 1) ? out[t >> 1] : in[t >> 1];
+    v.ptr = src[t]->ptr;
+    for (int i = 0; i < 4; ++i) v.s[i] = src[t]->stride[i];
+  }
+  const int heads[2] = {Hq, k_in ? Hk : 0};
+  cudaError_t e = rope_qk_launch(in, out, heads, B, L, D, base, offset, inverse, dtype, (cudaStream_t)stream);
+  return e == cudaSuccess ? FLA_OK : cuda_fail(e, "rotary embedding launch");
 }
 
 int fla_check_status(const int32_t* status, void* stream) {

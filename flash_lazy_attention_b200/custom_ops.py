@@ -6,6 +6,7 @@
     torch.ops.flash_lazy.entmax_attn_fwd / entmax_attn_bwd      adasplash, adasplash_no_block_mask
     torch.ops.flash_lazy.lazy_attn_fwd   / lazy_attn_bwd        lazy_attention_triton
     torch.ops.flash_lazy.entmax_rows_fwd / entmax_rows_bwd      triton_entmax
+    torch.ops.flash_lazy.rope_qk                                rotary embedding of q and k (its own backward)
 
 The public functions of ``ops`` route here while ``torch.compiler.is_compiling()``; in eager mode they keep using
 their ``autograd.Function``s (which allocate the SIMT family's aux buffers only when a backward will follow).
@@ -198,3 +199,28 @@ def _entmax_rows_backward(ctx, dy):
 
 
 entmax_rows_fwd.register_autograd(_entmax_rows_backward, setup_context=_entmax_rows_setup)
+
+
+# ---------------------------------------------------------------------------------------------
+# rotary position embedding of q and k
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("flash_lazy::rope_qk", mutates_args=(), device_types="cuda")
+def rope_qk(q: Tensor, k: Tensor, base: float, offset: int, inverse: bool) -> Tuple[Tensor, Tensor]:
+    return ops.rope_qk_apply(q, k, base, offset, inverse)
+
+
+@rope_qk.register_fake
+def _(q, k, base, offset, inverse):
+    return torch.empty_like(q), torch.empty_like(k)
+
+
+def _rope_setup(ctx, inputs, output):
+    ctx.base, ctx.offset, ctx.inverse = inputs[2], inputs[3], inputs[4]
+
+
+def _rope_backward(ctx, dq, dk):
+    gq, gk = rope_qk(dq, dk, ctx.base, ctx.offset, not ctx.inverse)   # the rotation is orthogonal
+    return gq, gk, None, None, None
+
+
+rope_qk.register_autograd(_rope_backward, setup_context=_rope_setup)

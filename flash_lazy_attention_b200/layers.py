@@ -19,11 +19,12 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .ops import lazy_attention_triton
+from .ops import lazy_attention_triton, rope_qk
 
 
 def rotary(x: torch.Tensor, base: float = 10000.0, offset: int = 0) -> torch.Tensor:
-    """Rotate-half rotary embedding of ``x`` [B, L, H, D] (positions offset..offset+L-1), computed in fp32."""
+    """Rotate-half rotary embedding of ``x`` [B, L, H, D] (positions offset..offset+L-1), computed in fp32: the
+    dense formulation of what ``ops.rope_qk`` does in one kernel (kept as its restatement for the tests)."""
     L, D = x.shape[1], x.shape[-1]
     half = D // 2
     inv = 1.0 / (base ** (torch.arange(half, device=x.device, dtype=torch.float32) / half))
@@ -73,9 +74,9 @@ class LazyAttentionLayer(nn.Module):
         q = self.q_proj(hidden_states).view(B, L, self.num_heads, self.head_dim)
         k = self.k_proj(hidden_states).view(B, L, self.num_kv_heads, self.head_dim)
         v = self.v_proj(hidden_states).view(B, L, self.num_kv_heads, self.head_dim)
-        q, k = rotary(q, self.rope_theta), rotary(k, self.rope_theta)
         # b l h d -> b h l d as views: the kernels take the strides
         q, k, v = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        q, k = rope_qk(q, k, self.rope_theta)     # one launch for both tensors
         o = lazy_attention_triton(q, k, v, self.bias.to(q.dtype), self.tau.to(q.dtype),
                                   window_size=self.max_bias_length, varlen=lengths_from(attention_mask, cu_seqlens))
         return self.o_proj(o.permute(0, 2, 1, 3).reshape(B, L, self.num_heads * self.head_dim))
@@ -98,8 +99,8 @@ class LazyAttention(nn.Module):
     def forward(self, x, attention_mask=None):
         B, L, _ = x.shape
         q, k, v = (proj(x).view(B, L, self.num_heads, self.head_dim) for proj in (self.q_proj, self.k_proj, self.v_proj))
-        q, k = rotary(q, self.rope_base), rotary(k, self.rope_base)
         q, k, v = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        q, k = rope_qk(q, k, self.rope_base)
         o = lazy_attention_triton(q, k, v, self.attention_biases, self.tau, window_size=self.window_size,
                                   varlen=lengths_from(attention_mask))
         return self.out_proj(o.permute(0, 2, 1, 3).reshape(B, L, self.dim))

@@ -453,6 +453,39 @@ def triton_entmax(x, alpha=1.5, n_iter=10, fast_math=True):
     return EntmaxFunc.apply(x, alpha, n_iter, fast_math)
 
 
+# ---------------------------------------------------------------------------------------------
+# rotary position embedding of q and k (the step before the attention operators in the layers)
+# ---------------------------------------------------------------------------------------------
+def rope_qk_apply(q, k, base=10000.0, offset=0, inverse=False):
+    """Rotate-half rotary embedding of q [B,H,L,D] and k [B,Hk,L,D] (views with unit inner stride) in one launch;
+    returns new tensors with the inputs' strides.  ``inverse`` rotates back (the gradient of the rotation)."""
+    lib = _lib.load()
+    for n, t in (("q", q), ("k", k)):
+        _check_cuda(t, n)
+        if t.dim() != 4:
+            raise ValueError(f"{n} must be [B, H, L, D]")
+    if q.dtype != k.dtype or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
+        raise ValueError("q and k must share dtype, batch, length and head dimension")
+
+    q, k = _unit_inner(q), _unit_inner(k)
+    B, H, L, D = q.shape
+    with torch.cuda.device(q.device):
+        qo, ko = torch.empty_like(q), torch.empty_like(k)
+        if qo.stride() != q.stride() or ko.stride() != k.stride():   # (overlapping or exotic views)
+            q, k = q.contiguous(), k.contiguous()
+            qo, ko = torch.empty_like(q), torch.empty_like(k)
+        rc = lib.fla_rope_qk(_t4(q), _t4(qo), H, _t4(k), _t4(ko), k.shape[1], B, L, D, _DTYPES[q.dtype], float(base),
+                             int(offset), int(bool(inverse)), _stream(q))
+        _lib.check(rc, "fla_rope_qk")
+    return qo, ko
+
+
+def rope_qk(q, k, base=10000.0, offset=0):
+    """Differentiable rotary embedding of q and k ([B,H,L,D] views; for ``b l h d`` tensors pass
+    ``x.transpose(1, 2)``), one kernel launch for both tensors."""
+    return torch.ops.flash_lazy.rope_qk(q, k, float(base), int(offset), False)
+
+
 def last_call_info() -> dict:
     """Kernel family the calling thread's last attention call ran on."""
     lib = _lib.load()

@@ -207,6 +207,20 @@ int fla_lazy_attn_bwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_te
                       int64_t dbias_stride, float* dtau, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* ---- rotary position embedding of q and k -----------------------------------------------------
+ * The step before the attention operators in the reference's layers (RotaryEmbedding of q and k,
+ * examples/lazy_attention_layer.py:131, examples/sw_attention_lazy.py:150), as one launch over both
+ * tensors.  Rotate-half convention over the head dimension: with x1 = x[..., :D/2], x2 = x[..., D/2:]
+ * and angle(l, j) = (l + offset) / base^(j / (D/2)) in fp32,
+ *   y1 = x1 cos - x2 sin,  y2 = x2 cos + x1 sin.
+ * q_*: [B,Hq,L,D] views, k_*: [B,Hk,L,D] views or both NULL; inner stride 1, D even (16-byte accesses
+ * when D is a multiple of 16 and bases and outer strides are 16-byte aligned, scalar ones otherwise);
+ * out may alias in (in place).  inverse != 0 rotates back, which is also the gradient of the
+ * rotation (it is orthogonal): dx = R^T dy.                                                   */
+int fla_rope_qk(const fla_tensor4* q_in, const fla_tensor4* q_out, int32_t Hq, const fla_tensor4* k_in,
+                const fla_tensor4* k_out, int32_t Hk, int32_t B, int32_t L, int32_t D, int32_t dtype,
+                float base, int32_t offset, int32_t inverse, void* stream);
+
 /* ---- self test of the tensor-core building blocks -----------------------------------------
  * No counterpart in the reference.  Computes C[128,128] (float) from bf16 A[128,128] and
  * B through one tcgen05 tile product, exercising one operand layout per `variant`:
