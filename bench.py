@@ -700,7 +700,9 @@ def main():
 
     if rank == 0:
         # library kernels per step: forward, dQ, dK/dV (tensor-core family); the SIMT family adds the delta pre-pass
-        launches_per_step = {"tcgen05": 3, "simt": 4}.get(path, 3)
+        # forward, dQ, dK/dV (the SIMT family adds its row pre-pass; a Lazy backward with trained bias and tau ends
+        # with the small kernel that converts the fixed-point dbias / dtau sums)
+        launches_per_step = {"tcgen05": 3, "simt": 4}.get(path, 3) + (1 if is_lazy and not args.frozen else 0)
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong" if args.partition else "weak",

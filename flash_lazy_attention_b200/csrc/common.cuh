@@ -46,6 +46,12 @@ struct AttnParams {
   float* dbias;
   int64_t dbias_stride;
   float* dtau;
+  // dbias and dtau are summed over the whole batch by many CTAs.  The kernels add into 64-bit fixed-point
+  // accumulators (integer addition is associative: the sums do not depend on the order in which the CTAs arrive),
+  // and a last small kernel converts them into the fp32 outputs above.  NULL: not wanted.
+  unsigned long long* dbias_acc;   // [H, dbias_acc_stride], distances < L
+  int64_t dbias_acc_stride;
+  unsigned long long* dtau_acc;    // [H]
   // backward scratch
   float* delta;  // [B,H,L]
   int flags;        // FLA_FLAG_* of fla_attn_geom
@@ -80,6 +86,13 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { retu
 // Round an fp32 value to the precision of T (what "P.to(v.dtype)" does before the PV product).
 template <typename T>
 __device__ __forceinline__ float round_to(float x) { return to_f32<T>(from_f32<T>(x)); }
+
+// Fixed-point form of a dbias / dtau contribution: 32 fractional bits (resolution 2.3e-10; the 64-bit range holds
+// sums up to 2e9 in magnitude).
+constexpr float kFixedScale = 4294967296.f;
+__device__ __forceinline__ unsigned long long to_fixed(float v) {
+  return (unsigned long long)__float2ll_rn(v * kFixedScale);
+}
 
 // ---- alpha-entmax scalar arithmetic -------------------------------------------------------
 // With e = 1/(alpha-1) and d = X - tau > 0:   p = d^e,  p' = d^(e-1),  p'' = d^(e-2).

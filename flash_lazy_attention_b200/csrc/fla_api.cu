@@ -21,6 +21,7 @@ cudaError_t simt_attn_bwd(int mode, const AttnParams& p, int dtype, cudaStream_t
 cudaError_t attn_delta(int mode, const AttnParams& p, int dtype, cudaStream_t st);
 cudaError_t entmax_rows_fwd(const void* x, void* y, int64_t rows, int64_t cols, float alpha, int n_iter, int fast,
                             int dtype, cudaStream_t st);
+cudaError_t lazy_params_finish(const AttnParams& p, cudaStream_t st);
 cudaError_t rope_qk_launch(const View4* in, const View4* out, const int* heads, int B, int L, int D, float base,
                            int offset, int inverse, int dtype, cudaStream_t st);
 cudaError_t entmax_rows_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t cols, float alpha,
@@ -409,7 +410,12 @@ int fla_lazy_attn_fwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_te
   return dispatch(LAZY, false, g, p, (cudaStream_t)stream);
 }
 
-size_t fla_lazy_attn_bwd_workspace(const fla_attn_geom* g) { return fla_entmax_attn_bwd_workspace(g); }
+// delta [B,H,L] floats, then the fixed-point accumulators of dbias [H, L] and dtau [H] (64-bit words)
+size_t fla_lazy_attn_bwd_workspace(const fla_attn_geom* g) {
+  const size_t rows = fla_entmax_attn_bwd_workspace(g);
+  if (rows == 0) return 0;
+  return rows + ((((size_t)g->H * ((size_t)g->L + 1)) * sizeof(unsigned long long) + 255) & ~(size_t)255);
+}
 
 int fla_lazy_attn_bwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_tensor4* k, const fla_tensor4* v,
                       const fla_tensor4* o, const fla_tensor4* dout, const float* bias, int64_t bias_stride,
@@ -439,16 +445,21 @@ int fla_lazy_attn_bwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_te
   p.dbias = dbias; p.dbias_stride = dbias_stride; p.dtau = dtau;
   p.delta = (float*)workspace;
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e;
-  if (dbias && window > 0) {
-    e = cudaMemset2DAsync(dbias, dbias_stride * sizeof(float), 0, (size_t)window * sizeof(float), g->H, st);
-    if (e != cudaSuccess) return cuda_fail(e, "clearing dbias");
+  const bool params = dbias != nullptr || dtau != nullptr;
+  if (params) {
+    // order-independent sums: the kernels add into 64-bit fixed-point accumulators behind delta, cleared here,
+    // and lazy_params_finish turns them into dbias / dtau (which it overwrites)
+    unsigned long long* acc = (unsigned long long*)((char*)workspace + fla_entmax_attn_bwd_workspace(g));
+    p.dbias_acc = dbias ? acc : nullptr;
+    p.dbias_acc_stride = g->L;
+    p.dtau_acc = dtau ? acc + (size_t)g->H * g->L : nullptr;
+    cudaError_t e = cudaMemsetAsync(acc, 0, ((size_t)g->H * ((size_t)g->L + 1)) * sizeof(unsigned long long), st);
+    if (e != cudaSuccess) return cuda_fail(e, "clearing the dbias / dtau accumulators");
   }
-  if (dtau) {
-    e = cudaMemsetAsync(dtau, 0, (size_t)g->H * sizeof(float), st);
-    if (e != cudaSuccess) return cuda_fail(e, "clearing dtau");
-  }
-  return dispatch(LAZY, true, g, p, st);
+  const int rc = dispatch(LAZY, true, g, p, st);
+  if (rc != FLA_OK || !params) return rc;
+  cudaError_t e = lazy_params_finish(p, st);
+  return e == cudaSuccess ? FLA_OK : cuda_fail(e, "dbias / dtau finish launch");
 }
 
 int fla_selftest_umma(const void* a, const void* b, float* c, int variant, int32_t* status, void* stream) {

@@ -407,14 +407,14 @@ __global__ void __launch_bounds__(256) delta_kernel(AttnParams p) {
     }
     if (lane == 0) p.delta[bh * L + i] = delta;
   }
-  if (MODE == LAZY && p.dtau != nullptr) {
+  if (MODE == LAZY && p.dtau_acc != nullptr) {
     if (lane == 0) s_dtau[warp] = contrib;
     __syncthreads();
     if (threadIdx.x == 0) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < 8; ++w) s += s_dtau[w];
-      if (s != 0.f) atomicAdd(p.dtau + h, s);
+      if (s != 0.f) atomicAdd(p.dtau_acc + h, to_fixed(s));
     }
   }
 }
@@ -455,7 +455,7 @@ __global__ void __launch_bounds__(NT) dq_kernel(AttnParams p) {
   float* Ks = dOs + BM * LD;
   float* Vs = Ks + BM * LD;
   float* dSs = Vs + BM * LD;
-  float* diag = dSs + BM * PLD;  // 128 floats: per-tile sums over the diagonals i-j
+  __shared__ unsigned long long diag[128];  // per-tile sums over the diagonals i-j, fixed point (see to_fixed)
 
   const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(NT) dq_kernel(AttnParams p) {
   }
   const float e = MODE == ENTMAX ? 1.f / (p.alpha - 1.f) : 0.f;
   const float tau_head = MODE == LAZY ? p.tau_h[h] : 0.f;
-  const bool want_dbias = MODE == LAZY && p.dbias != nullptr;
+  const bool want_dbias = MODE == LAZY && p.dbias_acc != nullptr;
 
   float acc[4][NDC];
 #pragma unroll
@@ -503,7 +503,7 @@ __global__ void __launch_bounds__(NT) dq_kernel(AttnParams p) {
     __syncthreads();
     load_tile<T, NDC>(Ks, kb, p.k.s[2], kt * BN, len, D);
     load_tile<T, NDC>(Vs, vb, p.v.s[2], kt * BN, len, D);
-    if (want_dbias && tid < 128) diag[tid] = 0.f;
+    if (want_dbias && tid < 128) diag[tid] = 0ull;
     __syncthreads();
     score_tile<MODE, NDC>(p, Qs, Ks, h, row0, kt * BN, len, causal, ty, tx, X);
     gemm_nt<NDC>(dOs, Vs, dA, ty, tx);
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(NT) dq_kernel(AttnParams p) {
         dSs[(ty * 4 + a) * PLD + tx + 16 * c] = round_to<T>(ds);
         if (tile_in_window && ds != 0.f) {
           int j = kt * BN + tx + 16 * c;
-          atomicAdd(&diag[i - j - dbase], ds);
+          atomicAdd(&diag[i - j - dbase], to_fixed(ds));
         }
       }
     }
@@ -528,8 +528,8 @@ __global__ void __launch_bounds__(NT) dq_kernel(AttnParams p) {
     gemm_nn_acc<NDC>(dSs, Ks, acc, ty, tx);
     if (tile_in_window && tid < 127) {
       int w = dbase + tid;
-      float s = diag[tid];
-      if (w >= 0 && w < p.window && s != 0.f) atomicAdd(p.dbias + (int64_t)h * p.dbias_stride + w, s);
+      const unsigned long long s = diag[tid];
+      if (w >= 0 && w < p.window && s != 0ull) atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + w, s);
     }
   }
 #pragma unroll
@@ -712,6 +712,25 @@ cudaError_t simt_attn_fwd(int mode, const AttnParams& p, int dtype, cudaStream_t
 cudaError_t simt_attn_bwd(int mode, const AttnParams& p, int dtype, cudaStream_t st) {
   return mode == ENTMAX ? simt::launch_dtype<ENTMAX>(p, dtype, true, st)
                         : simt::launch_dtype<LAZY>(p, dtype, true, st);
+}
+
+// Last step of a Lazy Attention backward with trained parameters: the fixed-point accumulators become the fp32
+// gradients (columns of dbias at or beyond L cannot be reached by any distance i - j and are zero).
+__global__ void lazy_params_finish_kernel(AttnParams p) {
+  const int h = blockIdx.y;
+  const int w = blockIdx.x * blockDim.x + threadIdx.x;
+  const double inv = 1.0 / (double)kFixedScale;
+  if (p.dbias != nullptr && w < p.window) {
+    const long long a = w < p.dbias_acc_stride ? (long long)p.dbias_acc[(int64_t)h * p.dbias_acc_stride + w] : 0ll;
+    p.dbias[(int64_t)h * p.dbias_stride + w] = (float)((double)a * inv);
+  }
+  if (p.dtau != nullptr && w == 0) p.dtau[h] = (float)((double)(long long)p.dtau_acc[h] * inv);
+}
+
+cudaError_t lazy_params_finish(const AttnParams& p, cudaStream_t st) {
+  dim3 grid((max(p.window, 1) + 255) / 256, p.H);
+  lazy_params_finish_kernel<<<grid, 256, 0, st>>>(p);
+  return cudaGetLastError();
 }
 
 // Row pre-pass of the backward; used by both kernel families.

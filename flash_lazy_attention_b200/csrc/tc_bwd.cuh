@@ -136,7 +136,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   auto k_slot = [](int g) { return g % NK; };
   auto k_phase = [](int g) { return (uint32_t)((g / NK) & 1); };
   __shared__ BwdShared sh;
-  __shared__ float dbias_s[MODE == LAZY ? kDbiasSmem : 1];
+  __shared__ unsigned long long dbias_s[MODE == LAZY ? kDbiasSmem : 1];   // fixed point, see to_fixed
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool causal = (MODE == LAZY) ? true : (p.causal != 0);
@@ -153,7 +153,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   const int row0 = mt * 128;
   const bool tile_live = row0 < len;
   const int nkt = tile_live ? (causal ? min((len + 127) >> 7, mt + 1) : ((len + 127) >> 7)) : 0;
-  const bool want_dbias = MODE == LAZY && p.dbias != nullptr;
+  const bool want_dbias = MODE == LAZY && p.dbias_acc != nullptr;
   volatile int* abort_flag = &sh.abort_flag;
   if (tid == 0) kernel_clock(status, 1, false);
 
@@ -184,7 +184,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
                                   : p.block_mask + ((int64_t)bh * nmt + mt) * p.mask_words, lane);
     if (lane == 0) sh.nact = n;
   }
-  if (MODE == LAZY) for (int w = tid; w < kDbiasSmem; w += kBwdThreads) dbias_s[w] = 0.f;
+  if (MODE == LAZY) for (int w = tid; w < kDbiasSmem; w += kBwdThreads) dbias_s[w] = 0ull;
   if (warp == kBwdProducerWarp) tmem_alloc(&sh.tmem_base, 512);
   tc_fence_before_sync();
   __syncthreads();
@@ -408,11 +408,11 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           delta = (live && sb > 0.f) ? sa / sb : 0.f;
         } else {
           delta = live ? sa : 0.f;
-          if (p.dtau != nullptr && quad == 0) {     // dtau_h += sum_i r_i / (i+1)
+          if (p.dtau_acc != nullptr && quad == 0) {     // dtau_h += sum_i r_i / (i+1)
             float contrib = live ? sb / (float)(i + 1) : 0.f;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
-            if (lane == 0 && contrib != 0.f) atomicAdd(p.dtau + h, contrib);
+            if (lane == 0 && contrib != 0.f) atomicAdd(p.dtau_acc + h, to_fixed(contrib));
           }
         }
         if (i < L && quad == 0) p.delta[bhl + i] = delta;
@@ -489,8 +489,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
               if (MODE == LAZY && want_dbias && in_window && ds != 0.f) {
                 const int dist = i - (kt * 128 + c0 + c);
                 if (dist < p.window) {   // dist >= 0 wherever ds != 0
-                  if (dist < kDbiasSmem) atomicAdd(&dbias_s[dist], ds);
-                  else atomicAdd(p.dbias + (int64_t)h * p.dbias_stride + dist, ds);
+                  if (dist < kDbiasSmem) atomicAdd(&dbias_s[dist], to_fixed(ds));
+                  else atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + dist, to_fixed(ds));
                 }
               }
             }
@@ -528,8 +528,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         named_bar_sync(1, kBwdRowThreads);
         const int wmax = min(p.window, kDbiasSmem);
         for (int w = tid; w < wmax; w += kBwdRowThreads) {
-          const float s = dbias_s[w];
-          if (s != 0.f) atomicAdd(p.dbias + (int64_t)h * p.dbias_stride + w, s);
+          const unsigned long long s = dbias_s[w];
+          if (s != 0ull) atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + w, s);
         }
       }
     } else if (i < L) {

@@ -198,7 +198,10 @@ size_t fla_lazy_attn_bwd_workspace(const fla_attn_geom* g);
 /* fla_lazy_attn_bwd replaces _lazy_attention_backward (lazy_attention_triton.py:585-667) and,
  * with dbias == dtau == NULL, _lazy_attention_backward_fast (:670-745).
  * dbias: float [H, window] (row stride dbias_stride), dtau: float [H]; both are overwritten
- * (not accumulated), summed over the batch.                                                */
+ * (not accumulated), summed over the batch.  The sums are formed in 64-bit fixed point (32
+ * fractional bits) inside the workspace and converted at the end, so they do not depend on the
+ * order in which thread blocks arrive: repeated calls give bit-identical dbias and dtau, like
+ * the reference's per-block buffers reduced in a fixed order (lazy_attention_triton.py:645-649). */
 int fla_lazy_attn_bwd(const fla_attn_geom* g, const fla_tensor4* q, const fla_tensor4* k,
                       const fla_tensor4* v, const fla_tensor4* o, const fla_tensor4* dout,
                       const float* bias, int64_t bias_stride, const float* tau, int32_t window,

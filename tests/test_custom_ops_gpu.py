@@ -73,10 +73,8 @@ def test_compiled_lazy_attention_and_rows_equal_eager():
 
     eager = _grads(f, (q, k, v, bias, tau), do)
     compiled = _grads(torch.compile(f, backend="aot_eager", fullgraph=True), (q, k, v, bias, tau), do)
-    for name, a, b in zip(("out", "dq", "dk", "dv"), eager[:4], compiled[:4]):
+    for name, a, b in zip(("out", "dq", "dk", "dv", "dbias", "dtau"), eager, compiled):
         assert torch.equal(a, b), (name, maxdiff(a, b))
-    for name, a, b in zip(("dbias", "dtau"), eager[4:], compiled[4:]):     # float atomics: order-dependent last bits
-        assert maxdiff(a, b) <= 1e-3 * max(1.0, float(a.abs().max())), (name, maxdiff(a, b))
 
     x, dy = torch.randn(64, 1000, device="cuda"), torch.randn(64, 1000, device="cuda")
     g = lambda t: fla.triton_entmax(t, alpha=1.5)     # noqa: E731

@@ -107,3 +107,22 @@ def test_bf16_params_cast_like_the_example_layers():
     out = lazy_attention_triton(q, k, v, bias.to(q.dtype), tau.to(q.dtype), window_size=W)
     out.backward(do)
     assert bias.grad.dtype == torch.float32 and bias.grad.shape == bias.shape and tau.grad.shape == tau.shape
+
+
+@pytest.mark.parametrize("path,dtype", [("simt", torch.float32), ("auto", torch.bfloat16)])
+def test_parameter_gradients_repeat_bit_for_bit(path, dtype):
+    """dbias and dtau are sums over the whole batch formed by many thread blocks; they are accumulated in fixed
+    point, so the order of arrival cannot change them (the reference reduces per-block buffers in a fixed order,
+    lazy_attention_triton.py:645-649)."""
+    set_path(path)
+    B, H, L, D, W = 3, 4, 1500, 64, 700
+    q, k, v, do = (randn((B, H, L, D), dtype, s) for s in (1, 2, 3, 4))
+    bias = randn((H, W), torch.float32, 5, scale=0.3)
+    tau = torch.tensor([-1.0, 0.3, -4.0, -0.5], device="cuda")
+    vl = torch.tensor([1500, 1111, 640], dtype=torch.int32, device="cuda")
+    first = _run(q, k, v, bias, tau, do, W, vl)
+    assert float(first[4].abs().max()) > 0 and float(first[5].abs().max()) > 0
+    for _ in range(3):
+        again = _run(q, k, v, bias, tau, do, W, vl)
+        for nm, a, b in zip(["out", "dq", "dk", "dv", "dbias", "dtau"], first, again):
+            assert torch.equal(a, b), (nm, maxdiff(a, b))
