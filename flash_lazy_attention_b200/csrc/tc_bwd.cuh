@@ -353,16 +353,24 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           unpack2(sa, acc_a0, acc_a1);
           unpack2(sb, acc_b0, acc_b1);
         } else if (MODE == LAZY && !need_mask && !in_window) {
-          // interior tile (no masked entry, no bias): straight-line arithmetic, no branches
+          // interior tile (no masked entry, no bias): straight-line arithmetic on pairs (packed f32x2 operations
+          // halve the issue slots of everything but the two exponentials and the two comparisons)
+          uint64_t sa = pack2(acc_a0, acc_a1), sb = pack2(acc_b0, acc_b1);
+          const uint64_t c2 = pack2(c1, c1), n2 = pack2(nrs, nrs), t2 = pack2(tau_row, tau_row);
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
-            const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, nrs));
-            const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
-            const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
-            const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
-            acc_a0 = fmaf(w0, md0, acc_a0); acc_b0 += md0;
-            acc_a1 = fmaf(w1, md1, acc_a1); acc_b1 += md1;
+            float x0, x1, t0, t1;
+            unpack2(fma2(pack2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), c2, n2), x0, x1);
+            const uint64_t ww = pack2(fast_exp2(x0), fast_exp2(x1));
+            unpack2(add2(ww, t2), t0, t1);
+            // M dP: a product with 1 or 0 (every dP of an interior tile is finite)
+            const uint64_t md = mul2(pack2(t0 > 0.f ? 1.f : 0.f, t1 > 0.f ? 1.f : 0.f),
+                                     pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])));
+            sa = fma2(ww, md, sa);
+            sb = add2(sb, md);
           }
+          unpack2(sa, acc_a0, acc_a1);
+          unpack2(sb, acc_b0, acc_b1);
         } else {
 #pragma unroll
           for (int x = 0; x < 32; ++x) {
@@ -457,13 +465,17 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           }
         } else if (MODE == LAZY && !need_mask && !in_window) {
           // interior tile: no masked entry, no bias and hence no dbias contribution
+          const uint64_t c2 = pack2(c1, c1), n2 = pack2(nrs, nrs), t2 = pack2(tau_row, tau_row), nd = pack2(-delta, -delta);
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
-            const float w0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, nrs));
-            const float w1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, nrs));
-            const float md0 = (w0 + tau_row > 0.f) ? __uint_as_float(gq[x]) : 0.f;
-            const float md1 = (w1 + tau_row > 0.f) ? __uint_as_float(gq[x + 1]) : 0.f;
-            pk[x >> 1] = pack16<FMT>(w0 * (md0 - delta), w1 * (md1 - delta));
+            float x0, x1, t0, t1, d0, d1;
+            unpack2(fma2(pack2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), c2, n2), x0, x1);
+            const uint64_t ww = pack2(fast_exp2(x0), fast_exp2(x1));
+            unpack2(add2(ww, t2), t0, t1);
+            const uint64_t md = mul2(pack2(t0 > 0.f ? 1.f : 0.f, t1 > 0.f ? 1.f : 0.f),
+                                     pack2(__uint_as_float(gq[x]), __uint_as_float(gq[x + 1])));
+            unpack2(mul2(ww, add2(md, nd)), d0, d1);
+            pk[x >> 1] = pack16<FMT>(d0, d1);
           }
         } else {
 #pragma unroll

@@ -216,7 +216,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       // The statistics of a tile's 128 query rows are fetched one tile ahead (threads 0-127, one row
       // each): the loads from global memory are in flight while the previous tile is worked on.
       // entmax keeps the negated values: they are the addends of  x = s*c1 - tau  and  dP - delta.
-      const float sgn = MODE == ENTMAX ? -1.f : 1.f;
+      const float sgn = -1.f;   // the row statistic and delta are staged negated: both only ever get subtracted
       float nx_stat = 0.f, nx_delta = 0.f;
       auto fetch_stats = [&](int n) {
         if (tid < 128 && n < nq) {
@@ -268,15 +268,18 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
             pk[x >> 1] = pack16<FMT>(w[x] * w[x], w[x + 1] * w[x + 1]);
           }
         } else if (fast) {
-          // lazy, interior tile: no masked entry and no bias, straight-line arithmetic
-          mmask = 0u;
+          // lazy, interior tile: no masked entry and no bias, straight-line arithmetic on pairs.  w keeps the
+          // softmax probability with the ReLU mask in its sign (negative: A = 0 there), which is all phase 2 needs.
+          const uint64_t c2 = pack2(c1, c1);
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
-            w[x] = fast_exp2(fmaf(__uint_as_float(r[x]), c1, -s0[x]));
-            w[x + 1] = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, -s0[x + 1]));
-            const float t0 = w[x] + s2[x], t1 = w[x + 1] + s2[x + 1];
-            mmask |= (t0 > 0.f ? 1u : 0u) << x;
-            mmask |= (t1 > 0.f ? 1u : 0u) << (x + 1);
+            float x0, x1, t0, t1;
+            unpack2(fma2(pack2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), c2,
+                         *reinterpret_cast<const uint64_t*>(s0 + x)), x0, x1);
+            const float w0 = fast_exp2(x0), w1 = fast_exp2(x1);
+            unpack2(add2(pack2(w0, w1), *reinterpret_cast<const uint64_t*>(s2 + x)), t0, t1);
+            w[x] = t0 > 0.f ? w0 : -w0;
+            w[x + 1] = t1 > 0.f ? w1 : -w1;
             pk[x >> 1] = pack16<FMT>(fmaxf(t0, 0.f), fmaxf(t1, 0.f));
           }
         } else {
@@ -297,7 +300,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                   const int dist = q0 + c - j;
                   if (dist >= 0 && dist < p.window) xs = fmaf(__ldg(p.bias + (int64_t)h * p.bias_stride + dist), kLog2e, xs);
                 }
-                xs -= s0[x + y];
+                xs += s0[x + y];
               }
               const bool valid = !need_mask || (c >= cmin && c <= cmax);
               float pv, wv;
@@ -331,6 +334,16 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                                                       *reinterpret_cast<const uint64_t*>(s1 + x))), d0, d1);
             pk[x >> 1] = pack16<FMT>(d0, d1);
           }
+        } else if (fast) {
+          // lazy, interior tile: dS = P (M dP - delta), M in the sign of w (every dP of an interior tile is finite)
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            float e0, e1;
+            const uint64_t md = mul2(pack2(w[x] > 0.f ? 1.f : 0.f, w[x + 1] > 0.f ? 1.f : 0.f),
+                                     pack2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])));
+            unpack2(add2(md, *reinterpret_cast<const uint64_t*>(s1 + x)), e0, e1);
+            pk[x >> 1] = pack16<FMT>(fabsf(w[x]) * e0, fabsf(w[x + 1]) * e1);
+          }
         } else {
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
@@ -341,7 +354,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
               const bool valid = (vmask >> (x + y)) & 1u, m = (mmask >> (x + y)) & 1u;
               // masked entries: exactly zero, whatever dP holds there (padding may be NaN)
               dsv[y] = MODE == ENTMAX ? (m ? w[x + y] * (dp + s1[x + y]) : 0.f)
-                                      : (valid ? w[x + y] * ((m ? dp : 0.f) - s1[x + y]) : 0.f);
+                                      : (valid ? w[x + y] * ((m ? dp : 0.f) + s1[x + y]) : 0.f);
             }
             pk[x >> 1] = pack16<FMT>(dsv[0], dsv[1]);
           }

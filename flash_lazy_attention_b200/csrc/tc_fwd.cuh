@@ -1019,13 +1019,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               if (lane == 0) mbar_arrive(&sh.s_free[buf]);
             }
             float tmax = -INFINITY;
-            if (!in_window && !need_mask) {   // interior tile: no bias, no masked entry
+            if (!in_window && !need_mask) {
+              // interior tile (no bias, no masked entry): the maximum is taken over the raw scores (the scale is
+              // positive), the scale is folded into the exponent's fused multiply-add, pairs go through packed
+              // f32x2 operations
+              float rmax = -INFINITY;
 #pragma unroll
-              for (int x = 0; x < 32; ++x) {
-                const float v = __uint_as_float(r[x]) * sl2;
-                r[x] = __float_as_uint(v);
-                tmax = fmaxf(tmax, v);
+              for (int x = 0; x < 32; ++x) rmax = fmaxf(rmax, __uint_as_float(r[x]));
+              const float mn = fmaxf(m, rmax * sl2);
+              if (mn > -INFINITY) {
+                const uint64_t s2 = pack2(sl2, sl2), nm = pack2(-mn, -mn);
+                uint64_t acc = pack2(0.f, 0.f);
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                  float x0, x1;
+                  unpack2(fma2(pack2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), s2, nm), x0, x1);
+                  acc = add2(acc, pack2(fast_exp2(x0), fast_exp2(x1)));
+                }
+                l = l * fast_exp2(m - mn) + sum2(acc);
+                m = mn;
               }
+              continue;
             } else
 #pragma unroll
             for (int x = 0; x < 32; ++x) {
