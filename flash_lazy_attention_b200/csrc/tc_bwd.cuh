@@ -478,6 +478,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             pk[x >> 1] = pack16<FMT>(d0, d1);
           }
         } else {
+          const bool dbias_tile = MODE == LAZY && want_dbias && in_window;   // the same for the whole CTA
+          float diag_a = 0.f, diag_b = 0.f;
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
             float dsv[2];
@@ -498,15 +500,31 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
               // masked entries: exactly zero, whatever dP holds there (padding may be NaN)
               const float ds = MODE == ENTMAX ? (m ? w * (dp - delta) : 0.f) : (valid ? w * ((m ? dp : 0.f) - delta) : 0.f);
               dsv[y] = ds;
-              if (MODE == LAZY && want_dbias && in_window && ds != 0.f) {
+              if (MODE == LAZY && dbias_tile) {
+                // dbias: sums of dS along the diagonals i - j.  The lanes of a warp are 32 consecutive rows, so
+                // for column c the lanes hold 32 consecutive distances; rotating the column by c lanes brings
+                // the entries of one diagonal to one lane: lane l collects distance base + l from the lanes that
+                // did not wrap around and base + l - 32 from those that did (fixed order: reproducible sums),
+                // and the warp ends the tile with 64 shared-memory additions instead of 1024.
                 const int dist = i - (kt * 128 + c0 + c);
-                if (dist < p.window) {   // dist >= 0 wherever ds != 0
-                  if (dist < kDbiasSmem) atomicAdd(&dbias_s[dist], to_fixed(ds));
-                  else atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + dist, to_fixed(ds));
-                }
+                const float dm = dist < p.window ? ds : 0.f;   // (ds = 0 wherever dist < 0: causal)
+                const float got = __shfl_sync(0xffffffffu, dm, (lane + c) & 31);
+                if (lane + c < 32) diag_a += got; else diag_b += got;
               }
             }
             pk[x >> 1] = pack16<FMT>(dsv[0], dsv[1]);
+          }
+          if (MODE == LAZY && dbias_tile) {
+            const int base = row0 + (warp & 3) * 32 - kt * 128 - c0;   // distance of (lane 0, column 0)
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              const float sum = part == 0 ? diag_a : diag_b;
+              const int dist = base + lane - 32 * part;
+              if (sum != 0.f && dist >= 0 && dist < p.window) {
+                if (dist < kDbiasSmem) atomicAdd(&dbias_s[dist], to_fixed(sum));
+                else atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + dist, to_fixed(sum));
+              }
+            }
           }
         }
         tmem_st16(t_dp, pk);
