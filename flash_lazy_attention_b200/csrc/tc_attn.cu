@@ -84,7 +84,7 @@ cudaError_t launch_fwd_shape(const CUtensorMap& mq, const CUtensorMap& mk, const
 
 template <int MODE, int D>
 constexpr size_t bwd_smem_bytes() {   // Q, dO, the K slots, two V slots
-  return (size_t)tc::TileCfg<D>::kTileBytes * (4 + tc::BwdRing<MODE>::kKSlots) + 1024;
+  return (size_t)tc::TileCfg<D>::kTileBytes * (4 + tc::kBwdKSlots) + 1024;
 }
 
 struct BwdMaps {

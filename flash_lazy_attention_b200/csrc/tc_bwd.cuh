@@ -28,7 +28,6 @@ constexpr int kBwdThreads = 640;
 constexpr int kBwdRowThreads = 512;   // warps 0-15, four threads per tile row
 constexpr int kBwdRowWarps = 16;
 constexpr int kBwdProducerWarp = 16;  // warps 17, 18 and 19 issue the products
-constexpr int kDbiasSmem = 2048;  // window distances accumulated in shared memory per CTA
 
 constexpr int kBwdMaxTiles = 512;     // key tiles per row of the tile list: L <= 65536
 
@@ -47,8 +46,9 @@ struct BwdShared {
 // waited for the dQ product of the tile before the previous one and the tensor pipe idled for the
 // copy's latency; a third slot takes that wait off the chain.  It fits next to the resident Q and dO
 // tiles and two V slots (7 tiles = 224 KB at D = 128) only because this kernel keeps almost nothing
-// else in shared memory; the Lazy variant, which also holds the dbias window, stays at two.
-template <int MODE> struct BwdRing { static constexpr int kKSlots = MODE == ENTMAX ? 3 : 2; };
+// else in shared memory: the Lazy variant's dbias sums go from the warps straight to the fixed-point
+// accumulators in global memory (64 additions per warp and window tile, see the second sweep).
+constexpr int kBwdKSlots = 3;
 
 // Key tiles a query block has to visit: all of them, or -- with a block mask from the forward --
 // those holding a non-zero probability (two 64-key mask bits per 128-key tile).  Run by one warp;
@@ -131,12 +131,11 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   uint8_t* smem = align_1024(smem_raw);
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + Cfg::kTileBytes;
-  constexpr int NK = BwdRing<MODE>::kKSlots;
+  constexpr int NK = kBwdKSlots;
   uint8_t* ring = smem + 2 * Cfg::kTileBytes;  // NK slots for K tiles, then two for V tiles
   auto k_slot = [](int g) { return g % NK; };
   auto k_phase = [](int g) { return (uint32_t)((g / NK) & 1); };
   __shared__ BwdShared sh;
-  __shared__ unsigned long long dbias_s[MODE == LAZY ? kDbiasSmem : 1];   // fixed point, see to_fixed
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool causal = (MODE == LAZY) ? true : (p.causal != 0);
@@ -184,7 +183,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
                                   : p.block_mask + ((int64_t)bh * nmt + mt) * p.mask_words, lane);
     if (lane == 0) sh.nact = n;
   }
-  if (MODE == LAZY) for (int w = tid; w < kDbiasSmem; w += kBwdThreads) dbias_s[w] = 0ull;
   if (warp == kBwdProducerWarp) tmem_alloc(&sh.tmem_base, 512);
   tc_fence_before_sync();
   __syncthreads();
@@ -505,7 +503,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
                 // for column c the lanes hold 32 consecutive distances; rotating the column by c lanes brings
                 // the entries of one diagonal to one lane: lane l collects distance base + l from the lanes that
                 // did not wrap around and base + l - 32 from those that did (fixed order: reproducible sums),
-                // and the warp ends the tile with 64 shared-memory additions instead of 1024.
+                // and the warp ends the tile with 64 additions to the accumulators in global memory.
                 const int dist = i - (kt * 128 + c0 + c);
                 const float dm = dist < p.window ? ds : 0.f;   // (ds = 0 wherever dist < 0: causal)
                 const float got = __shfl_sync(0xffffffffu, dm, (lane + c) & 31);
@@ -520,10 +518,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             for (int part = 0; part < 2; ++part) {
               const float sum = part == 0 ? diag_a : diag_b;
               const int dist = base + lane - 32 * part;
-              if (sum != 0.f && dist >= 0 && dist < p.window) {
-                if (dist < kDbiasSmem) atomicAdd(&dbias_s[dist], to_fixed(sum));
-                else atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + dist, to_fixed(sum));
-              }
+              if (sum != 0.f && dist >= 0 && dist < p.window)
+                atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + dist, to_fixed(sum));
             }
           }
         }
@@ -552,14 +548,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             w.w = (live && nact > 0) ? pack16<FMT>(__uint_as_float(r[x + 6]) * p.scale, __uint_as_float(r[x + 7]) * p.scale) : 0u;
             *(uint4*)(grow + (quad * (D / 4) + x) * 2) = w;
           }
-        }
-      }
-      if (want_dbias) {
-        named_bar_sync(1, kBwdRowThreads);
-        const int wmax = min(p.window, kDbiasSmem);
-        for (int w = tid; w < wmax; w += kBwdRowThreads) {
-          const unsigned long long s = dbias_s[w];
-          if (s != 0ull) atomicAdd(p.dbias_acc + (int64_t)h * p.dbias_acc_stride + w, s);
         }
       }
     } else if (i < L) {
