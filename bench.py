@@ -71,7 +71,7 @@ class ClockSampler:
 
     def __init__(self, gpu_id: str):
         # nvidia-smi orders GPUs by PCI bus and ignores CUDA_VISIBLE_DEVICES: select by UUID
-        self.index, self.rows, self.proc = gpu_id, [], None
+        self.index, self.rows, self.stamps, self.proc, self.note = gpu_id, [], [], None, None
 
     def __enter__(self):
         try:
@@ -89,6 +89,14 @@ class ClockSampler:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) >= 6 and parts[0].isdigit():
                 self.rows.append(parts)
+                self.stamps.append(time.monotonic())
+
+    def window(self, t0, t1):
+        """Keep the samples read between t0 and t1 (host monotonic seconds); returns how many there are."""
+        keep = [i for i, t in enumerate(self.stamps[:len(self.rows)]) if t0 <= t <= t1]
+        self.rows = [self.rows[i] for i in keep]
+        self.stamps = [self.stamps[i] for i in keep]
+        return len(self.rows)
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -105,8 +113,11 @@ class ClockSampler:
         busy = [x for x in sm if x > 0.5 * max(sm)] or sm
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons,
-                "samples": len(sm), "gpu": self.index}
+        out = {"sm_mhz": statistics.median(busy), "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons,
+               "samples": len(sm), "gpu": self.index}
+        if self.note:
+            out["sampled"] = self.note
+        return out
 
 
 def cpu_reference(L, D, alpha, causal, steps, warmup, threads=None, B=1, H=1, median=False):
@@ -423,20 +434,33 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    fla.read_status(dev, reset=True)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the sampler starts before the warm-up (nvidia-smi needs up to a second for its first line on an 8-GPU box);
+    # only the samples read during the timed region count
     with ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) as clocks:
+        for _ in range(args.warmup):
+            step()
         barrier()
+        fla.read_status(dev, reset=True)
+        barrier()
+        t_start = time.monotonic()
         ev0.record()
         for _ in range(args.steps):
             step()
         ev1.record()
         barrier()
+        t_end = time.monotonic()
+        status = fla.read_status(dev)
+        if clocks.window(t_start, t_end + 0.05) < 2:
+            # a timed region shorter than two sampling periods: the same steps again, untimed, for the sampler
+            clocks.rows, clocks.stamps = [], []
+            t_more = time.monotonic()
+            while time.monotonic() - t_more < 0.7:
+                step()
+                torch.cuda.synchronize()
+            clocks.window(t_more + 0.1, time.monotonic() + 0.05)
+            clocks.note = "the same steps repeated untimed right after the timed region (it was shorter than two samples)"
     ms = ev0.elapsed_time(ev1) / args.steps
-    status = fla.read_status(dev)
     if status["error"]:
         raise RuntimeError(f"a kernel reported an expired wait: {status}")
     path = fla.last_call_info()["path"]
@@ -511,7 +535,7 @@ def main():
     # kernels and are split evenly: dQ kernel 1 + 1, dK/dV kernel 2 + 1.
     unit = F_fwd / 2.0
     credit = {"fwd": 2.0, "dq": 2.0, "dkdv": 3.0}
-    labels = {"fwd": "forward kernel (row max + candidate lists, S, P.V)", "dq": "dQ kernel (delta sweep, S, dP, dQ)",
+    labels = {"fwd": "forward kernel (row max, row thresholds, S, P.V)", "dq": "dQ kernel (delta sweep, S, dP, dQ)",
               "dkdv": "dK/dV kernel (S^T, dP^T, dV, dK)"}
     traffic_file = os.path.join(ROOT, "profiles", "dram_traffic.json")
     traffic_tab = {}
