@@ -878,7 +878,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             const uint32_t first_grp = sn & 1u;
             int nact_pass = 0;
             for (int w = 0; w * 32 < nkt; ++w) nact_pass += __popc(((volatile uint32_t*)sh.act[rpass & 1u])[w]);
-            if ((uint32_t)grp != first_grp) named_bar_arrive(4 + (int)first_grp, kFwdRowThreads);
+            // (general alpha: no turns.  Its arithmetic is a long dependent chain per entry on a divergent path, and
+            // four warps per scheduler hide that latency better than two.)
+            constexpr bool kTurns = KIND != 2;
+            if (kTurns && (uint32_t)grp != first_grp) named_bar_arrive(4 + (int)first_grp, kFwdRowThreads);
             for_my_tiles(rpass, [&](int kt, uint32_t cs) {
               const uint32_t buf = cs & 3;
               bool hit = false;           // some entry of this tile lies above tau
@@ -904,7 +907,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 for (int x = 0; x < 64; ++x)
                   if (x > climit) r[x] = 0xff800000u;   // -inf
               }
-              noff += __uint_as_float(named_bar_sync_token(4 + grp, kFwdRowThreads));   // my turn
+              if (kTurns) noff += __uint_as_float(named_bar_sync_token(4 + grp, kFwdRowThreads));   // my turn
               TRACE((tid & 127) == 0 && half == 0, 0, kt, 6, trace_clock_dep(noff, noff, noff));
               if (KIND == 0 && !FLA_DBG(p, 1)) {
                 // alpha = 1.5: d <= 1 on the whole bracket, so one saturating fma yields max(d, 0)
@@ -950,13 +953,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               }
               TRACE((tid & 127) == 0 && half == 0, 0, kt, 7, trace_clock_dep(a0, a1, a2));
               // hand the turn over once the sums are done (the sums feed the barrier's memory clobber)
-              named_bar_arrive_after(4 + (grp ^ 1), kFwdRowThreads, a0 + b0, a1 + b1, a2 + b2);
+              if (kTurns) named_bar_arrive_after(4 + (grp ^ 1), kFwdRowThreads, a0 + b0, a1 + b1, a2 + b2);
               hit_bits |= (hit ? 1u : 0u) << (kt & 31);
             });
             {
               // the group that did not sum last consumes the turn that is left over
               const uint32_t last_grp = (first_grp + (uint32_t)nact_pass + 1u) & 1u;
-              if (nact_pass > 0 ? (uint32_t)grp != last_grp : (uint32_t)grp == first_grp) named_bar_sync(4 + grp, kFwdRowThreads);
+              if (kTurns && (nact_pass > 0 ? (uint32_t)grp != last_grp : (uint32_t)grp == first_grp)) named_bar_sync(4 + grp, kFwdRowThreads);
             }
             publish_hits();
             sh.part[quad][0][row] = a0 + b0;
