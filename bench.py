@@ -316,6 +316,9 @@ def main():
                     help="entmax workloads: q, k drawn around this many well separated centres in contiguous "
                          "segments of --seg tokens, so that most (query block, key block) pairs are empty")
     ap.add_argument("--seg", type=int, default=512, help="segment length of --clusters")
+    ap.add_argument("--flags", type=int, default=0,
+                    help="fla_attn_geom.flags for the run (include/fla.h: 1 thresholds by passes over recomputed scores, "
+                         "4 by candidates kept in the row-max pass; 0 = the library's choice)")
     ap.add_argument("--partition", action="store_true",
                     help="strong scaling: ONE seeded problem of the workload's size, its (batch, head) pairs split over "
                          "the ranks (no collective in the timed region); afterwards the ranks' results are gathered "
@@ -355,6 +358,7 @@ def main():
             os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     _lib.check(_lib.load().fla_device_supported(local), "device check")
+    fla.set_flags(args.flags)
 
     B, H, L, D, alpha, causal = WORKLOADS[args.workload]
     if args.alpha is not None and alpha is not None:
