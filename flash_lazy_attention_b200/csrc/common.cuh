@@ -55,15 +55,8 @@ struct AttnParams {
   // backward scratch
   float* delta;  // [B,H,L]
   int flags;        // FLA_FLAG_* of fla_attn_geom
-  int debug;        // development builds (-DFLA_TRACE) only: timing switches; always 0 in the shipped library
 };
 
-// Timing switches exist only in development builds; the shipped kernels contain none of them.
-#ifdef FLA_TRACE
-#define FLA_DBG(p, bit) (((p).debug & (bit)) != 0)
-#else
-#define FLA_DBG(p, bit) false
-#endif
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

@@ -134,16 +134,6 @@ static void fill_common(AttnParams& p, const fla_attn_geom* g) {
   p.varlen = g->varlen;
   p.scale = 1.0f / sqrtf((float)g->D);
   p.flags = g->flags;
-#ifdef FLA_TRACE
-  // Development builds only: FLA_DEBUG (read once) switches single pieces of the tensor-core kernels
-  // off for timing experiments; results are wrong with most of them.  The shipped library has none.
-  //   1   forward threshold passes: skip the row arithmetic        2   ... skip the score products
-  //   4   forward: exactly five threshold passes
-  //   32  backward: do not launch the dK/dV kernel                 64  ... the dQ kernel
-  //   256 forward: the row-max pass marks every tile
-  static const int dbg = [] { const char* v = getenv("FLA_DEBUG"); return v ? atoi(v) : 0; }();
-  p.debug = dbg;
-#endif
 }
 
 // Runs `mode` forward or backward on the family the geometry selects.

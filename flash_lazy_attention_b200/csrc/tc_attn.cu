@@ -111,10 +111,10 @@ cudaError_t launch_bwd(const BwdMaps& m, const AttnParams& p, int* status, cudaS
   const unsigned grid_kv = (unsigned)(((p.L + 127) / 128) * p.B * p.Hkv);   // one CTA per key tile of a kv head
   // dq_kernel first: its first sweep produces the row scalars delta that dkdv_kernel reads
   // (development builds can leave out one of the two launches for timing experiments)
-  if (!FLA_DBG(p, 64)) kq<<<grid, tc::kBwdThreads, smem, st>>>(mq, mk, mv, mdo, p, status);
+  kq<<<grid, tc::kBwdThreads, smem, st>>>(mq, mk, mv, mdo, p, status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  if (!FLA_DBG(p, 32)) kkv<<<grid_kv, tc::kKvThreads, smem_kv, st>>>(mq, mk, mv, mdo, p, status);
+  kkv<<<grid_kv, tc::kKvThreads, smem_kv, st>>>(mq, mk, mv, mdo, p, status);
   return cudaGetLastError();
 }
 
@@ -180,8 +180,3 @@ cudaError_t tc_attn_bwd(int mode, const AttnParams& p, int dtype, int* status, c
 
 }  // namespace fla
 
-#ifdef FLA_TRACE
-extern "C" int fla_trace_read(long long* out, int n) {
-  return (int)cudaMemcpyFromSymbol(out, fla::tc::g_fwd_trace, (size_t)n * 8);
-}
-#endif

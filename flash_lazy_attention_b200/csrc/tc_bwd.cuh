@@ -87,11 +87,6 @@ __device__ __forceinline__ void prob_terms(float x, float e, float tau_row, bool
   }
 }
 
-#ifdef FLA_TRACE
-#define DQTRACE(cond, idx, slot) do { if (blockIdx.x == 0 && (cond) && (idx) < 128) g_fwd_trace[(idx) * 16 + (slot)] = trace_clock(); } while (0)
-#else
-#define DQTRACE(cond, idx, slot) do { } while (0)
-#endif
 
 // D[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory as four pieces of 16 columns (16-bit
 // pairs), piece q at a_tmem + 32 q (each of the four threads of a row writes its 32 reduction elements inside
@@ -225,12 +220,9 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       if (role < 2) {
         for (int g = 0; g < nact; ++g) {
           const int j = g & 1;
-          DQTRACE(true, g, role == 0 ? 0 : 4);
           ok = ok && (role == 0 ? mbar_wait(&sh.k_full[k_slot(g)], k_phase(g), abort_flag, status, 42)
                                 : mbar_wait(&sh.v_full[j], (g >> 1) & 1, abort_flag, status, 42));
-          DQTRACE(true, g, role == 0 ? 1 : 5);
           ok = ok && mbar_wait(&sh.t_free[j], ((g >> 1) & 1) ^ 1, abort_flag, status, 43);
-          DQTRACE(true, g, role == 0 ? 2 : 6);
           tc_fence_after_sync();
           if (ok) {
             if (role == 0) issue_nt<D, FMT>(tmem + 256 * j, q_addr, k_addr(g));
@@ -238,7 +230,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           }
           umma_commit(&sh.t_full[j]);
           umma_commit(role == 0 ? &sh.k_empty[k_slot(g)] : &sh.v_empty[j]);
-          DQTRACE(true, g, role == 0 ? 3 : 7);
         }
       }
       // the second sweep lays tensor memory out differently: every first-sweep tile must be read
@@ -247,30 +238,22 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       if (role == 0) {
         for (int t = 0; t < nact; ++t) {
           const int g = nact + t;
-          DQTRACE(true, g, 0);
           ok = ok && mbar_wait(&sh.k_full[k_slot(g)], k_phase(g), abort_flag, status, 45);
-          DQTRACE(true, g, 1);
           ok = ok && mbar_wait(&sh.s_free, (t & 1) ^ 1, abort_flag, status, 46);   // S of tile t-1 is in registers
-          DQTRACE(true, g, 2);
           tc_fence_after_sync();
           if (ok) issue_nt<D, FMT>(tmem, q_addr, k_addr(g));
           umma_commit(&sh.s_full);
-          DQTRACE(true, g, 3);
         }
       } else if (role == 1) {
         for (int t = 0; t < nact; ++t) {
           const int g = nact + t, bsel = t & 1;
-          DQTRACE(true, g, 4);
           ok = ok && mbar_wait(&sh.v_full[g & 1], (g >> 1) & 1, abort_flag, status, 47);
-          DQTRACE(true, g, 5);
           // dS of tile t-2 has been consumed before its buffer receives dP of tile t
           if (t >= 2) ok = ok && mbar_wait(&sh.dq_done[bsel], ((t - 2) >> 1) & 1, abort_flag, status, 48);
-          DQTRACE(true, g, 6);
           tc_fence_after_sync();
           if (ok) issue_nt<D, FMT>(tmem + 128 + 128 * bsel, do_addr, v_addr(g));
           umma_commit(&sh.dp_full[bsel]);
           umma_commit(&sh.v_empty[g & 1]);
-          DQTRACE(true, g, 7);
         }
       } else {
         for (int t = 0; t < nact; ++t) {   // dQ += dS(t) . K(t)
@@ -285,7 +268,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           if (ok) issue_tn_quads<D, FMT>(tmem_acc, tmem + 128 + 128 * bsel, k_addr(g), t > 0, nks);
           umma_commit(&sh.dq_done[bsel]);
           umma_commit(&sh.k_empty[k_slot(g)]);
-          DQTRACE(true, g, 12);
         }
         umma_commit(&sh.acc_full);
       }
@@ -316,9 +298,7 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         const bool need_mask = kt * 128 + 127 > tile_jlim;
         const int climit = jlim - kt * 128 - c0;
         const bool in_window = MODE == LAZY && (row0 - kt * 128 - 127 < p.window);
-        DQTRACE(tid == 0, g, 8);
         mbar_wait(&sh.t_full[j], (g >> 1) & 1, abort_flag, status, 52);
-        DQTRACE(tid == 0, g, 9);
         __syncwarp();
         tc_fence_after_sync();
         const uint32_t t_s = tmem + lane_base + 256 * j + c0, t_dp = t_s + 128;
@@ -336,7 +316,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           nrs = __uint_as_float(mbar_arrive_token(&sh.t_free[j])) - rstat;   // (token: see mbar_arrive_token)
           if (g == nact - 1) mbar_arrive(&sh.sweep_done);
         }
-        DQTRACE(tid == 0, g, 10);
         if (MODE == ENTMAX && KIND == 0 && !need_mask) {
           // alpha = 1.5, no masked entry: U = max(x, 0) by one saturating fma; packed sums
           uint64_t sa = pack2(acc_a0, acc_a1), sb = pack2(acc_b0, acc_b1);
@@ -393,7 +372,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           }
         }
       }
-      DQTRACE(tid == 0, nact - 1, 11);
       if (nact == 0 && lane == 0) mbar_arrive(&sh.sweep_done);
       // The four threads of a row meet in tensor memory: all own the same lane.  Columns 384..391
       // are free from the moment every row thread has read the last first-sweep tile (the first
@@ -431,7 +409,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         const int climit = jlim - kt * 128 - c0;
         const bool in_window = MODE == LAZY && (row0 - kt * 128 - 127 < p.window);
         const uint32_t t_s = tmem + lane_base + c0, t_dp = tmem + lane_base + 128 + 128 * bsel + c0;
-        DQTRACE(tid == 0, nact + t, 8);
         // S has a single buffer, so this thread's columns go to registers as soon as they exist and the
         // buffer is handed back before dP is even waited for; the S product of the next tile then
         // overlaps the rest of this one.
@@ -446,11 +423,9 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         float nrs = -rstat;
         if (lane == 0) nrs = __uint_as_float(mbar_arrive_token(&sh.s_free)) - rstat;
         mbar_wait(&sh.dp_full[bsel], (t >> 1) & 1, abort_flag, status, 55);
-        DQTRACE(tid == 0, nact + t, 9);
         __syncwarp();
         tc_fence_after_sync();
         tmem_ld32_sync(t_dp, gq);
-        DQTRACE(tid == 0, nact + t, 10);
         if (MODE == ENTMAX && KIND == 0 && !need_mask) {
           const uint64_t nd = pack2(-delta, -delta);
 #pragma unroll
@@ -528,7 +503,6 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.ds_full[bsel]);
-        DQTRACE(tid == 0, nact + t, 11);
       }
       mbar_wait(&sh.acc_full, 0, abort_flag, status, 56);   // (committed even when no tile was visited)
       __syncwarp();

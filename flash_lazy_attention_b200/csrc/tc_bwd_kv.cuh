@@ -152,12 +152,9 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         for (int n = 0; n < nq; ++n) {
           const int s = n % kKvStages;
           const uint32_t q_addr = ring_addr + s * 2 * Cfg::kTileBytes, do_addr = q_addr + Cfg::kTileBytes;
-          DQTRACE(true, n, 0);
           ok = ok && mbar_wait(&sh.ring_full[s], (n / kKvStages) & 1, abort_flag, status, 62);
-          DQTRACE(true, n, 1);
           // S^T(n) over P^T(n-1): free once dV(n-1) has read it
           if (n > 0) ok = ok && mbar_wait(&sh.dv_done, (n - 1) & 1, abort_flag, status, 63);
-          DQTRACE(true, n, 2);
           tc_fence_after_sync();
           if (ok) issue_nt<D, FMT>(tmem, k_addr, q_addr);                 // S^T  = K . Q^T
           umma_commit(&sh.s_full);
@@ -166,16 +163,13 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
           tc_fence_after_sync();
           if (ok) issue_nt<D, FMT>(tmem_dp, v_addr, do_addr);             // dP^T = V . dO^T
           umma_commit(&sh.dp_full);
-          DQTRACE(true, n, 3);
         }
         if (status) atomicAdd((unsigned long long*)(status + 4), (unsigned long long)(2 * nq));
       } else {
         for (int n = 0; n < nq; ++n) {
           const int s = n % kKvStages;
           const uint32_t q_addr = ring_addr + s * 2 * Cfg::kTileBytes, do_addr = q_addr + Cfg::kTileBytes;
-          DQTRACE(true, n, 4);
           ok = ok && mbar_wait(&sh.p_full, n & 1, abort_flag, status, 64);
-          DQTRACE(true, n, 5);
           tc_fence_after_sync();
           // query rows beyond the end of the sequence: padding rows of Q and dO stay out of the
           // reductions (the score products of this tile have completed), see zero_tail_rows
@@ -193,7 +187,6 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
           if (ok) issue_tn_quads<D, FMT>(tmem_dk, tmem_dp, q_addr, n > 0, nks);      // dK += dS^T . Q
           umma_commit(&sh.dk_done);
           umma_commit(&sh.ring_empty[s]);
-          DQTRACE(true, n, 6);
         }
         umma_commit(&sh.acc_full);
         if (status) atomicAdd((unsigned long long*)(status + 4), (unsigned long long)(2 * nq));
@@ -253,9 +246,7 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         uint32_t vmask = 0xffffffffu, mmask = 0xffffffffu;   // general path: valid entries / support
         uint32_t r[32], pk[16];
         // ---- phase 1: S^T -> P^T ---------------------------------------------------------------
-        DQTRACE((tid & 127) == 0 && quad == 0, n, 8);
         mbar_wait(&sh.s_full, n & 1, abort_flag, status, 66);
-        DQTRACE((tid & 127) == 0 && quad == 0, n, 9);
         __syncwarp();
         tc_fence_after_sync();
         tmem_ld32_sync(t_s, r);
@@ -319,10 +310,8 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.p_full);
-        DQTRACE((tid & 127) == 0 && quad == 0, n, 10);
         // ---- phase 2: dP^T -> dS^T ---------------------------------------------------------------
         mbar_wait(&sh.dp_full, n & 1, abort_flag, status, 69);
-        DQTRACE((tid & 127) == 0 && quad == 0, n, 11);
         __syncwarp();
         tc_fence_after_sync();
         tmem_ld32_sync(t_dp, r);
@@ -364,7 +353,6 @@ dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.ds_full);
-        DQTRACE((tid & 127) == 0 && quad == 0, n, 12);
       }
       mbar_wait(&sh.acc_full, 0, abort_flag, status, 67);   // (committed even when no tile was visited)
       __syncwarp();

@@ -169,27 +169,6 @@ constexpr float kListTolHalley = 1e-3f;
 constexpr float kListTolNewton = 1e-4f;
 constexpr float kListTol = 1e-5f;
 
-#ifdef FLA_TRACE
-// Development instrumentation (builds with -DFLA_TRACE only; see timeline.py of the package): CTA 0
-// records clock64 values into a device array that fla_trace_read copies out.
-//   marks   g_fwd_trace[2016 + i]: i = 0 kernel start, i = 1.. verdict of pass i-1 published,
-//           30 row threads done with the last pass, 31 output accumulator complete
-//   table 1 first threshold pass, per key tile: [0..3] issuer: loop start, K tile landed, score
-//           buffer free, product issued; [4..7] row thread 0 of the tile's group: wait start, scores
-//           ready, turn granted, sums done
-//   table 2 last pass, per visited tile: [0..3] score issuer: start, K landed, buffer free, issued;
-//           [4..7] row thread: start, scores ready, probability buffer free, probabilities written
-//   table 3 last pass: [0..3] P.V issuer: start, V landed, probabilities ready, issued
-// (table t starts at (t-1) * 512; 64 tiles x 8 slots each; the backward kernels use the same array, 128 entries x 16 slots)
-__device__ long long g_fwd_trace[64 * 8 * 4];
-__device__ __forceinline__ long long trace_clock() { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) :: "memory"); return t; }
-__device__ __forceinline__ long long trace_clock_dep(float a, float b, float c) { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) : "f"(a), "f"(b), "f"(c) : "memory"); return t; }
-#define TRACE_PASS(idx) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (idx) < 32) g_fwd_trace[64 * 8 * 4 - 32 + (idx)] = trace_clock(); } while (0)
-#define TRACE(cond, table_, kt, slot, val) do { if (blockIdx.x == 0 && (cond) && (table_) >= 1 && (table_) <= 3 && (kt) < 64) g_fwd_trace[(((table_) - 1) * 64 + (kt)) * 8 + (slot)] = (val); } while (0)
-#else
-#define TRACE_PASS(idx) do { } while (0)
-#define TRACE(cond, pass_, kt, slot, val) do { } while (0)
-#endif
 
 
 // 8-byte shared-memory accesses that are not cached in registers: other warps write these pairs.
@@ -432,17 +411,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for_each_tile(pass, [&](int kt) {
           if ((sn & 1u) == me) {
             const uint32_t sb = sn & 3u;   // four score buffers in flight
-            TRACE(true, pass == 0 ? 1 : 0, kt, 0, trace_clock());
             const uint32_t st = rp.stage();
             bool ok = mbar_wait(&sh.ring_full[st], rp.phase(), abort_flag, status, 21);
-            TRACE(true, pass == 0 ? 1 : 0, kt, 1, trace_clock());
             ok = ok && mbar_wait(&sh.s_free[sb], ((sn >> 2) & 1u) ^ 1u, abort_flag, status, 22);
-            TRACE(true, pass == 0 ? 1 : 0, kt, 2, trace_clock());
             tc_fence_after_sync();
-            if (ok && !FLA_DBG(p, 2)) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
+            if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
             umma_commit(&sh.ring_empty[st]);
             umma_commit(&sh.s_full[sb]);
-            TRACE(true, pass == 0 ? 1 : 0, kt, 3, trace_clock());
             ++issued;
           }
           rp.advance();
@@ -473,28 +448,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t sb = (uint32_t)t & 1u;
         const uint32_t ofs = score_role ? fin_k_ofs(t) : fin_v_ofs(t, nfin);
         const uint32_t st = rp.stage_at(ofs);
-        TRACE(true, score_role ? 2 : 3, t, 0, trace_clock());
         bool ok = mbar_wait(&sh.ring_full[st], rp.phase_at(ofs), abort_flag, status, 24 + me);
-        TRACE(true, score_role ? 2 : 3, t, 1, trace_clock());
         if (score_role) {
           // the row threads have read S(t-2) out of this buffer (their probabilities live elsewhere)
           if (t >= 2) ok = ok && mbar_wait(&sh.p_full[sb], ((t - 2) >> 1) & 1, abort_flag, status, 28);
-          TRACE(true, 2, t, 2, trace_clock());
           tc_fence_after_sync();
           if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
           umma_commit(&sh.ring_empty[st]);
           umma_commit(&sh.f_full[sb]);
-          TRACE(true, 2, t, 3, trace_clock());
         } else {
           ok = ok && mbar_wait(&sh.p_full[sb], (t >> 1) & 1, abort_flag, status, 26);
-          TRACE(true, 3, t, 2, trace_clock());
           tc_fence_after_sync();
           int nks = 8;
           if (ok && tail_visited && t == nfin - 1) nks = zero_tail_rows(ring + st * Cfg::kTileBytes, tail_valid, Cfg::kBoxes, 128);
           if (ok) issue_tn<D, FMT, FMT>(tmem_o, tmem + kProbCol + sb * 64, ring_addr + st * Cfg::kTileBytes, t > 0, nks);
           umma_commit(&sh.ring_empty[st]);
           umma_commit(&sh.pv_done[sb]);
-          TRACE(true, 3, t, 3, trace_clock());
         }
         ++issued;
       }
@@ -503,7 +472,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     }
     __syncwarp();
   } else {
-    TRACE_PASS(0);
     // ------------------------------------------------------------------ row threads
     // Sixteen warps.  Tiles alternate between two groups (group g owns the score buffers g and
     // g + 2, i.e. every tile whose running index is congruent to g mod 2); inside a group two
@@ -536,7 +504,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       auto signal_pass = [&](bool cont) {
         if (tid == 0) {
           if (signalled > 0) mbar_wait(&sh.pass_ack, (signalled - 1u) & 1u, abort_flag, status, 35);
-          TRACE_PASS(signalled + 1);
           ++signalled;
           *(volatile int*)&sh.cont_flag = cont ? 1 : 0;
           __threadfence_block();
@@ -613,9 +580,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for_my_tiles(0, [&](int kt, uint32_t cs) {
           const uint32_t buf = cs & 3;
           if ((kt >> 5) != mark_word) { publish_marks(); mark_word = kt >> 5; }
-          TRACE((tid & 127) == 0 && half == 0, 1, kt, 4, trace_clock());
           mbar_wait(&sh.s_full[buf], (cs >> 2) & 1, abort_flag, status, 30);
-          TRACE((tid & 127) == 0 && half == 0, 1, kt, 5, trace_clock());
           __syncwarp();
           tc_fence_after_sync();
           uint32_t r[64];
@@ -623,7 +588,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           tc_fence_before_sync();
           __syncwarp();   // every lane holds its scores: one arrival per warp
           if (lane == 0) mbar_arrive(&sh.s_free[buf]);
-          TRACE((tid & 127) == 0 && half == 0, 1, kt, 6, trace_clock());
           if (kt * 128 + 127 > tile_jlim) {
             const int climit = jlim - kt * 128 - c0;
 #pragma unroll
@@ -646,7 +610,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           }
           const bool near_max = tm > -INFINITY && (msh - tm) * c1 < 1.f;
           bool took = false;
-          if (LISTS && !lovf && !FLA_DBG(p, 2048)) {
+          if (LISTS && !lovf) {
             // raw-score form of the row's best lower bound; masked entries are -inf and never pass
             const float blb = fmaxf(fmaxf(rlb[row], rlb[128 + row]), fmaxf(rlb[256 + row], rlb[384 + row]));
             const float thr = fmaxf(msh - inv_c1, blb * inv_c1);
@@ -666,10 +630,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     : "memory");
               took |= sa != sa_in;
               if (__any_sync(0xffffffffu, sa - sa0 > (uint32_t)(kStageSlots - 8) * 2048u)) {
-#ifdef FLA_TRACE
-                if (lane == 0 && status) atomicAdd(status + 20, 1);
-#endif
-                if (FLA_DBG(p, 512)) sa = sa0; else
                 tighten(3, 0);
               }
             }
@@ -682,15 +642,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             const uint32_t third = ntile / 3u;
             const bool due = ntile <= 4u || (ntile & (ntile - 1u)) == 0u || (third * 3u == ntile && (third & (third - 1u)) == 0u);
             if (due) {
-#ifdef FLA_TRACE
-              if (lane == 0 && status) atomicAdd(status + 21, 1);
-#endif
-              if (!FLA_DBG(p, 1024))
               tighten(1, 8);
             }
           }
           mark_bits |= (((!LISTS || lovf) ? near_max : took) ? 1u : 0u) << (kt & 31);
-          TRACE((tid & 127) == 0 && half == 0, 1, kt, 7, trace_clock());
         });
         publish_marks();
         sh.part[quad][0][row] = mrow;
@@ -703,7 +658,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const int lo_t = lane * 32;
           const uint32_t full = nkt >= lo_t + 32 ? 0xffffffffu : (nkt > lo_t ? (1u << (nkt - lo_t)) - 1u : 0u);
           uint32_t nx = ((volatile uint32_t*)sh.act_next)[lane];
-          if (!__any_sync(0xffffffffu, nx != 0u) || FLA_DBG(p, 256)) nx = full;
+          if (!__any_sync(0xffffffffu, nx != 0u)) nx = full;
           sh.act[1][lane] = nx;
           sh.act_next[lane] = 0u;
         }
@@ -740,9 +695,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (tid == 0 && status) atomicAdd(status + 6, 1);
           const int n_st = (int)((sa - sa0) >> 11);
           const int npool = min(*(volatile int*)&sh.npool, kPoolSize);
-#ifdef FLA_TRACE
-          if (status) { atomicAdd(status + 23, n_st); if (tid == 0) atomicAdd(status + 22, npool); }
-#endif
           // start from the row's best lower bound (still left of the root)
           if (live && row_lb - m > ts) { ts = fminf(row_lb - m, hi); lo = ts; }
           for (int it = 0; it < p.niter; ++it) {
@@ -852,7 +804,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               if (fabs(zt - (double)ts) <= 1e-4) ts = (float)zt;
             }
           }
-          TRACE_PASS(29);
         } else {
           if (tid == 0 && status) atomicAdd(status + 7, 1);
           bool cont = p.niter > 0;
@@ -886,9 +837,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               const uint32_t buf = cs & 3;
               bool hit = false;           // some entry of this tile lies above tau
               if ((kt >> 5) != hit_word) { publish_hits(); hit_word = kt >> 5; }
-              TRACE((tid & 127) == 0 && half == 0, 0, kt, 4, trace_clock());
               mbar_wait(&sh.s_full[buf], (cs >> 2) & 1, abort_flag, status, 31);
-              TRACE((tid & 127) == 0 && half == 0, 0, kt, 5, trace_clock());
               __syncwarp();
               tc_fence_after_sync();
               // this thread's half row into registers, buffer handed back at once: the next product
@@ -908,8 +857,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                   if (x > climit) r[x] = 0xff800000u;   // -inf
               }
               if (kTurns) noff += __uint_as_float(named_bar_sync_token(4 + grp, kFwdRowThreads));   // my turn
-              TRACE((tid & 127) == 0 && half == 0, 0, kt, 6, trace_clock_dep(noff, noff, noff));
-              if (KIND == 0 && !FLA_DBG(p, 1)) {
+              if (KIND == 0) {
                 // alpha = 1.5: d <= 1 on the whole bracket, so one saturating fma yields max(d, 0)
                 // (and 0 for a masked entry); sums kept as packed pairs
                 uint64_t s0 = pack2(0.f, 0.f), s1 = s0, s2 = s0;
@@ -925,7 +873,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 const float cnt = sum2(s2);
                 a0 += sum2(s0); a1 += sum2(s1); a2 += cnt;
                 hit = cnt > 0.f;
-              } else if (!FLA_DBG(p, 1)) {
+              } else {
                 auto chunk_sums = [&](const uint32_t* rc) {
   #pragma unroll
                   for (int x = 0; x < 32; x += 2) {
@@ -947,11 +895,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 };
                 chunk_sums(r);
                 chunk_sums(r + 32);
-              } else {
-                a0 += __uint_as_float(r[0] ^ r[37] ^ r[63]);
-                hit = true;
               }
-              TRACE((tid & 127) == 0 && half == 0, 0, kt, 7, trace_clock_dep(a0, a1, a2));
               // hand the turn over once the sums are done (the sums feed the barrier's memory clobber)
               if (kTurns) named_bar_arrive_after(4 + (grp ^ 1), kFwdRowThreads, a0 + b0, a1 + b1, a2 + b2);
               hit_bits |= (hit ? 1u : 0u) << (kt & 31);
@@ -978,7 +922,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             }
             const bool all_done = named_bar_and(2, kFwdRowThreads, done);
             cont = !all_done && (it + 1 < p.niter) && !*abort_flag;
-            if (FLA_DBG(p, 4)) cont = it + 1 < 5;
             if (warp == 0) {
               // tiles of the next pass: those in which some row found an entry above its tau
               const int lo_t = lane * 32;
@@ -1099,12 +1042,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const uint32_t pbase = tgrp + kProbCol + grp * 64 + half * 32;   // my half of probability buffer grp
       sn = 0;
       for_my_tiles(rpass, [&](int kt, uint32_t u) {
-        TRACE((tid & 127) == 0 && half == 0, 2, u, 4, trace_clock());
         mbar_wait(&sh.f_full[grp], (u >> 1) & 1, abort_flag, status, 33);
-        TRACE((tid & 127) == 0 && half == 0, 2, u, 5, trace_clock());
         // the P.V product two tiles back must have read the probability buffer
         if (u >= 2) mbar_wait(&sh.pv_done[grp], ((u - 2) >> 1) & 1, abort_flag, status, 36);
-        TRACE((tid & 127) == 0 && half == 0, 2, u, 6, trace_clock());
         __syncwarp();
         tc_fence_after_sync();
         const bool need_mask = kt * 128 + 127 > tile_jlim;
@@ -1167,7 +1107,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.p_full[grp]);
-        TRACE((tid & 127) == 0 && half == 0, 2, u, 7, trace_clock());
         if (MODE == ENTMAX && p.block_mask != nullptr) {
           // key block (64 keys) 2 kt + half holds a non-zero probability for some row of this warp
           if (__any_sync(0xffffffffu, nz != 0) && lane == 0) {
@@ -1178,9 +1117,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       });
 
       // ---- epilogue: each of the four threads of a row stores 32 output columns -----------------
-      TRACE_PASS(30);
       mbar_wait(&sh.o_full, 0, abort_flag, status, 34);
-      TRACE_PASS(31);
       __syncwarp();
       tc_fence_after_sync();
       const bool in_range = i < L;
