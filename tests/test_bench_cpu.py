@@ -28,3 +28,19 @@ def test_non_zero_ranks_of_the_reference_arm_stay_silent():
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert res.returncode == 0 and res.stdout.strip() == ""
+
+
+def test_clock_sampler_keeps_only_the_samples_of_the_timed_region():
+    sys.path.insert(0, ROOT)
+    import bench
+    s = bench.ClockSampler("GPU-none")
+    s.rows = [["300", "1965", "Not Active", "Not Active", "Not Active", "Not Active"],       # before the region (idle)
+              ["1700", "1965", "Not Active", "Not Active", "Not Active", "Active"],
+              ["1720", "1965", "Not Active", "Not Active", "Not Active", "Active"],
+              ["210", "1965", "Active", "Not Active", "Not Active", "Not Active"]]            # after it
+    s.stamps = [1.0, 2.0, 2.1, 3.0]
+    assert s.window(1.5, 2.5) == 2
+    out = s.summary()
+    assert out["sm_mhz"] == 1710 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"] and out["samples"] == 2
+    s.rows, s.stamps = [], []
+    assert s.summary()["reasons"] == ["unavailable"]
