@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libflashlazy.so")
 FLA_F32, FLA_F16, FLA_BF16 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
 PATH_NAMES = {PATH_AUTO: "auto", PATH_SIMT: "simt", PATH_TCGEN05: "tcgen05"}
-FLAG_NO_CANDIDATE_LIST, FLAG_PLAIN_FIRST_STEP, FLAG_CANDIDATE_LIST = 1, 2, 4
+FLAG_NO_CANDIDATE_LIST, FLAG_PLAIN_FIRST_STEP, FLAG_CANDIDATE_LIST, FLAG_ONE_TILE_CTAS = 1, 2, 4, 8
 
 
 class Tensor4(C.Structure):

@@ -33,19 +33,21 @@ bool view_ok(const View4& v, const char** why) {
   return true;
 }
 
-template <int MODE, int D>
-constexpr size_t fwd_smem_bytes() {   // Q, the K/V ring; entmax: staging slots of the candidate lists
-  return (size_t)tc::TileCfg<D>::kTileBytes * (1 + tc::TileCfg<D>::kStages) + 1024 + (MODE == ENTMAX ? tc::kStageBytes : 0);
+template <int MODE, int D, bool LISTS, bool PAIR>
+constexpr size_t fwd_smem_bytes() {   // the query tile(s), the K/V ring; with kept candidates: their staging slots
+  return (size_t)tc::TileCfg<D>::kTileBytes * ((PAIR ? 2 : 1) + tc::TileCfg<D>::kStages) + 1024 +
+         ((MODE == ENTMAX && !PAIR) ? tc::kStageBytes : 0);
 }
 
-template <int MODE, int D, int FMT, int KIND, bool LISTS>
+template <int MODE, int D, int FMT, int KIND, bool LISTS, bool PAIR = false>
 cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        int* status, cudaStream_t st) {
-  auto kern = tc::fwd_kernel<MODE, D, FMT, KIND, LISTS>;
-  constexpr size_t smem = fwd_smem_bytes<MODE, D>();
+  auto kern = tc::fwd_kernel<MODE, D, FMT, KIND, LISTS, PAIR>;
+  constexpr size_t smem = fwd_smem_bytes<MODE, D, LISTS, PAIR>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  const unsigned grid = (unsigned)(((p.L + 127) / 128) * p.B * p.H);
+  const int nmt = (p.L + 127) / 128;
+  const unsigned grid = (unsigned)((PAIR ? (nmt + 1) / 2 : nmt) * p.B * p.H);
   kern<<<grid, tc::kFwdThreads, smem, st>>>(mq, mk, mv, p, status);
   return cudaGetLastError();
 }
@@ -61,6 +63,16 @@ cudaError_t launch_fwd_kind(const CUtensorMap& mq, const CUtensorMap& mk, const 
     const int kind = alpha_kind(p.alpha);
     const bool lists = (p.flags & FLA_FLAG_NO_CANDIDATE_LIST) ? false
                                                                : (kind == 1 || (p.flags & FLA_FLAG_CANDIDATE_LIST) != 0);
+    // thresholds by score passes: two query tiles per CTA share every K tile they fetch (FLA_FLAG_ONE_TILE_CTAS
+    // keeps the one-tile form)
+    const bool pair = !lists && !(p.flags & FLA_FLAG_ONE_TILE_CTAS);
+    if (pair) {
+      switch (kind) {
+        case 0: return launch_fwd<MODE, D, FMT, 0, false, true>(mq, mk, mv, p, status, st);
+        case 1: return launch_fwd<MODE, D, FMT, 1, false, true>(mq, mk, mv, p, status, st);
+        default: return launch_fwd<MODE, D, FMT, 2, false, true>(mq, mk, mv, p, status, st);
+      }
+    }
     switch (kind) {
       case 0: return lists ? launch_fwd<MODE, D, FMT, 0, true>(mq, mk, mv, p, status, st)
                            : launch_fwd<MODE, D, FMT, 0, false>(mq, mk, mv, p, status, st);

@@ -59,7 +59,7 @@ struct TileCfg {
 };
 
 struct FwdShared {
-  uint64_t q_full, ring_full[8], ring_empty[8], s_full[4], s_free[4], f_full[2], p_full[2], pv_done[2], pass_done, o_full;
+  uint64_t q_full, ring_full[8], ring_empty[8], s_full[4], s_free[4], f_full[2], p_full[2], pv_done[2], pass_done, o_full, o_read;
   uint32_t tmem_base;
   int abort_flag;
   int cont_flag;
@@ -245,15 +245,23 @@ static __device__ __noinline__ TightenResult tighten_candidates(FwdShared* sh, f
 // LISTS: the entmax row-max pass keeps candidates and the thresholds are iterated on them (otherwise: by
 // passes over recomputed score tiles only).  A compile-time switch, because the candidate bookkeeping costs
 // the pass-only kernel registers it does not have.
-template <int MODE, int D, int FMT, int KIND, bool LISTS>
+// PAIR (entmax, thresholds by score passes only): one CTA holds TWO adjacent query tiles.  A K tile fetched from L2
+// then serves two score products -- the score passes are bound by that fetch -- and row group g works on the rows
+// of query tile g for every key tile (without PAIR the groups split the key tiles of one query tile between them).
+// With the running tile index t of a pass mapped to 2 t + g for group and issuer g, the buffer and barrier
+// arithmetic of the score passes is the same in both forms.  The last pass runs once per query tile, one after the
+// other (tensor memory holds one output accumulator).
+template <int MODE, int D, int FMT, int KIND, bool LISTS, bool PAIR = false>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const AttnParams p, int* status) {
   using Cfg = TileCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_1024(smem_raw);
+  static_assert(!PAIR || (MODE == ENTMAX && !LISTS), "the two-tile form exists for entmax score passes only");
+  constexpr int NQ = PAIR ? 2 : 1;   // query tiles of this CTA
   uint8_t* sQ = smem;
-  uint8_t* ring = smem + Cfg::kTileBytes;
+  uint8_t* ring = smem + NQ * Cfg::kTileBytes;
   uint8_t* stage = ring + Cfg::kStages * Cfg::kTileBytes;   // entmax only: candidate slots of the row threads
   __shared__ FwdShared sh;
 
@@ -266,19 +274,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   // All query tiles of one (batch, head) pair are adjacent in the grid, heaviest first: the CTAs in
   // flight at any time stream the same few K/V tensors, which therefore stay in the L2 cache.
   // (With the pair as the fast index every resident CTA would stream a different pair from HBM.)
-  const int bh = (int)(blockIdx.x / nmt);
-  const int mt = nmt - 1 - (int)(blockIdx.x % nmt);
+  const int ncta = PAIR ? (nmt + 1) >> 1 : nmt;    // CTAs per (batch, head) pair
+  const int bh = (int)(blockIdx.x / ncta);
+  const int mt = NQ * (ncta - 1 - (int)(blockIdx.x % ncta));   // (first) query tile of this CTA
   const int b = bh / p.H, h = bh % p.H;
   const int len = p.varlen ? min(max(p.varlen[b], 0), L) : L;
   const int row0 = mt * 128;
   const bool tile_live = row0 < len;
-  const int nkt = tile_live ? (causal ? min((len + 127) >> 7, mt + 1) : ((len + 127) >> 7)) : 0;
+  // key tiles the CTA visits: those the last of its live query tiles may look at
+  const int mt_hi = (PAIR && row0 + 128 < len) ? mt + 1 : mt;
+  const int nkt = tile_live ? (causal ? min((len + 127) >> 7, mt_hi + 1) : ((len + 127) >> 7)) : 0;
+  const int nsub = tile_live ? (mt_hi - mt + 1) : 0;   // live query tiles of this CTA
   volatile int* abort_flag = &sh.abort_flag;
   if (tid == 0) kernel_clock(status, 0, false);
 
   if (tid == 0) {
     mbar_init(&sh.q_full, 1);
-    for (int s = 0; s < 8; ++s) { mbar_init(&sh.ring_full[s], 1); mbar_init(&sh.ring_empty[s], 1); }
+    // (two-tile form: a K tile is released by the commits of both issuers; in its last passes the one issuer
+    // that reads a slot commits twice)
+    for (int s = 0; s < 8; ++s) { mbar_init(&sh.ring_full[s], 1); mbar_init(&sh.ring_empty[s], PAIR ? 2 : 1); }
     for (int s = 0; s < 4; ++s) {
       mbar_init(&sh.s_full[s], 1);
       mbar_init(&sh.s_free[s], kFwdBufWarps);
@@ -291,6 +305,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_init(&sh.pass_done, 1);
     mbar_init(&sh.pass_ack, 3);
     mbar_init(&sh.o_full, 1);
+    mbar_init(&sh.o_read, kFwdRowThreads / 32);
     sh.abort_flag = 0;
     sh.cont_flag = 0;
     fence_mbar_init();
@@ -361,8 +376,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
-      mbar_expect_tx(&sh.q_full, Cfg::kTileBytes);
+      mbar_expect_tx(&sh.q_full, NQ * Cfg::kTileBytes);
       tma_load_tile<D>(sQ, &map_q, &sh.q_full, row0, h, b);
+      if (PAIR) tma_load_tile<D>(sQ + Cfg::kTileBytes, &map_q, &sh.q_full, row0 + 128, h, b);   // (rows beyond L read as zeros)
       RingPos rp;
       uint32_t pass = 0;
       auto load = [&](const CUtensorMap* map, int kt, int tag) {
@@ -382,7 +398,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         mbar_arrive(&sh.pass_ack);
         if (!go_on || *abort_flag) break;
       }
-      {   // last pass: K(0), K(1), V(0), K(2), V(1), ..., V(n-1)
+      for (int sub = 0; sub < nsub; ++sub) {   // last pass (per query tile): K(0), K(1), V(0), K(2), V(1), ..., V(n-1)
         int prev = -1;
         for_each_tile(pass, [&](int kt) {
           load(&map_k, kt, 12);
@@ -409,13 +425,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       uint32_t sn = 0, pass = 0;
       while (true) {
         for_each_tile(pass, [&](int kt) {
-          if ((sn & 1u) == me) {
-            const uint32_t sb = sn & 3u;   // four score buffers in flight
+          if (PAIR || (sn & 1u) == me) {
+            const uint32_t vs = PAIR ? 2u * sn + me : sn;   // (two-tile form: every tile, for query tile `me`)
+            const uint32_t sb = vs & 3u;   // four score buffers in flight
             const uint32_t st = rp.stage();
             bool ok = mbar_wait(&sh.ring_full[st], rp.phase(), abort_flag, status, 21);
-            ok = ok && mbar_wait(&sh.s_free[sb], ((sn >> 2) & 1u) ^ 1u, abort_flag, status, 22);
+            ok = ok && mbar_wait(&sh.s_free[sb], ((vs >> 2) & 1u) ^ 1u, abort_flag, status, 22);
             tc_fence_after_sync();
-            if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
+            if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_addr + (PAIR ? me * Cfg::kTileBytes : 0u), ring_addr + st * Cfg::kTileBytes);
             umma_commit(&sh.ring_empty[st]);
             umma_commit(&sh.s_full[sb]);
             ++issued;
@@ -438,36 +455,48 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // depended on).
       int nfin = 0;
       for (int w = 0; w * 32 < nkt; ++w) nfin += __popc(((volatile uint32_t*)sh.act[pass & 1u])[w]);
-      const bool score_role = (sn & 1u) == me;
+      const bool score_role = PAIR ? me == 0u : (sn & 1u) == me;
       // the last key tile of the sequence may reach into its padding: if it is visited at all, it is
       // visited last (ascending order)
       const int tail_valid = len - (nkt - 1) * 128;
       const bool tail_visited = nkt > 0 && tail_valid < 128 &&
                                 ((((volatile uint32_t*)sh.act[pass & 1u])[(nkt - 1) >> 5] >> ((nkt - 1) & 31)) & 1u) != 0u;
-      for (int t = 0; t < nfin; ++t) {
-        const uint32_t sb = (uint32_t)t & 1u;
-        const uint32_t ofs = score_role ? fin_k_ofs(t) : fin_v_ofs(t, nfin);
-        const uint32_t st = rp.stage_at(ofs);
-        bool ok = mbar_wait(&sh.ring_full[st], rp.phase_at(ofs), abort_flag, status, 24 + me);
-        if (score_role) {
-          // the row threads have read S(t-2) out of this buffer (their probabilities live elsewhere)
-          if (t >= 2) ok = ok && mbar_wait(&sh.p_full[sb], ((t - 2) >> 1) & 1, abort_flag, status, 28);
-          tc_fence_after_sync();
-          if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
-          umma_commit(&sh.ring_empty[st]);
-          umma_commit(&sh.f_full[sb]);
-        } else {
-          ok = ok && mbar_wait(&sh.p_full[sb], (t >> 1) & 1, abort_flag, status, 26);
-          tc_fence_after_sync();
-          int nks = 8;
-          if (ok && tail_visited && t == nfin - 1) nks = zero_tail_rows(ring + st * Cfg::kTileBytes, tail_valid, Cfg::kBoxes, 128);
-          if (ok) issue_tn<D, FMT, FMT>(tmem_o, tmem + kProbCol + sb * 64, ring_addr + st * Cfg::kTileBytes, t > 0, nks);
-          umma_commit(&sh.ring_empty[st]);
-          umma_commit(&sh.pv_done[sb]);
+      // Two-tile form: the pass runs once per live query tile.  The barriers of buffer sb (f_full, p_full, pv_done)
+      // complete once per tile of parity sb, so tile t of run `sub` is use number sub * ceil or floor(nfin / 2) +
+      // t / 2 of its buffer, and the ring goes on from where the previous run left it.
+      for (int sub = 0; sub < (PAIR ? nsub : 1); ++sub) {
+        const uint32_t q_sub = q_addr + (uint32_t)sub * Cfg::kTileBytes;
+        for (int t = 0; t < nfin; ++t) {
+          const uint32_t sb = (uint32_t)t & 1u;
+          const uint32_t use = (uint32_t)sub * (uint32_t)((nfin + 1 - (int)sb) >> 1) + ((uint32_t)t >> 1);   // of buffer sb
+          const uint32_t ofs = score_role ? fin_k_ofs(t) : fin_v_ofs(t, nfin);
+          const uint32_t st = rp.stage_at(ofs);
+          bool ok = mbar_wait(&sh.ring_full[st], rp.phase_at(ofs), abort_flag, status, 24 + me);
+          if (score_role) {
+            // the row threads have read the previous S out of this buffer (their probabilities live elsewhere)
+            if (use >= 1u) ok = ok && mbar_wait(&sh.p_full[sb], (use - 1u) & 1u, abort_flag, status, 28);
+            tc_fence_after_sync();
+            if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_sub, ring_addr + st * Cfg::kTileBytes);
+            umma_commit(&sh.ring_empty[st]);
+            if (PAIR) umma_commit(&sh.ring_empty[st]);
+            umma_commit(&sh.f_full[sb]);
+          } else {
+            ok = ok && mbar_wait(&sh.p_full[sb], use & 1u, abort_flag, status, 26);
+            // the output accumulator of the previous query tile has been read out before it is overwritten
+            if (PAIR && sub > 0 && t == 0) ok = ok && mbar_wait(&sh.o_read, (uint32_t)(sub - 1) & 1u, abort_flag, status, 27);
+            tc_fence_after_sync();
+            int nks = 8;
+            if (ok && tail_visited && t == nfin - 1) nks = zero_tail_rows(ring + st * Cfg::kTileBytes, tail_valid, Cfg::kBoxes, 128);
+            if (ok) issue_tn<D, FMT, FMT>(tmem_o, tmem + kProbCol + sb * 64, ring_addr + st * Cfg::kTileBytes, t > 0, nks);
+            umma_commit(&sh.ring_empty[st]);
+            if (PAIR) umma_commit(&sh.ring_empty[st]);
+            umma_commit(&sh.pv_done[sb]);
+          }
+          ++issued;
         }
-        ++issued;
+        if (!score_role) umma_commit(&sh.o_full);
+        rp.pos += 2u * (uint32_t)nfin;
       }
-      if (!score_role) umma_commit(&sh.o_full);
       if (status) atomicAdd((unsigned long long*)(status + 4), issued);
     }
     __syncwarp();
@@ -484,7 +513,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const int quad = grp * 2 + half;
     const int c0 = half * 64;                  // first key column of this thread inside a tile
     const int row = (warp & 3) * 32 + lane;
-    const int i = row0 + row;
+    const int row0g = row0 + (PAIR ? grp * 128 : 0);   // first row of the query tile this thread's score passes work on
+    const int i = row0g + row;
     const bool live = i < len;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tgrp = tmem + lane_base;   // + 128 * buffer index
@@ -493,7 +523,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // key j is valid for this row iff j <= jlim
       const int jlim = live ? (causal ? min(i, len - 1) : len - 1) : -1;
       // tiles whose last key exceeds this bound hold masked entries for some row
-      const int tile_jlim = (row0 + 127 < len) ? (causal ? row0 : len - 1) : -1;
+      const int tile_jlim = (row0g + 127 < len) ? (causal ? row0g : len - 1) : -1;
       uint32_t sn = 0;    // running tile index at the start of the current pass
       uint32_t rpass = 0; // index of the current pass
       float rstat = 0.f;  // tau (entmax) or base-2 log-sum-exp (lazy)
@@ -515,7 +545,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         uint32_t run = sn;
         for_each_tile(pass, [&](int kt) {
           const uint32_t cs = run++;
-          if ((cs & 1u) == (uint32_t)grp) fn(kt, cs);
+          if (PAIR) fn(kt, 2u * cs + (uint32_t)grp);   // every tile, for this group's query tile
+          else if ((cs & 1u) == (uint32_t)grp) fn(kt, cs);
         });
         sn = run;
       };
@@ -651,8 +682,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         sh.part[quad][0][row] = mrow;
         sh.part[quad][1][row] = tlb;
         named_bar_sync(1, kFwdRowThreads);
-        float m = fmaxf(fmaxf(sh.part[0][0][row], sh.part[1][0][row]), fmaxf(sh.part[2][0][row], sh.part[3][0][row]));
-        const float row_lb = fmaxf(fmaxf(sh.part[0][1][row], sh.part[1][1][row]), fmaxf(sh.part[2][1][row], sh.part[3][1][row]));
+        // (two-tile form: a row belongs to the two threads of one group)
+        float m = PAIR ? fmaxf(sh.part[2 * grp][0][row], sh.part[2 * grp + 1][0][row])
+                       : fmaxf(fmaxf(sh.part[0][0][row], sh.part[1][0][row]), fmaxf(sh.part[2][0][row], sh.part[3][0][row]));
+        const float row_lb = PAIR ? fmaxf(sh.part[2 * grp][1][row], sh.part[2 * grp + 1][1][row])
+                                  : fmaxf(fmaxf(sh.part[0][1][row], sh.part[1][1][row]), fmaxf(sh.part[2][1][row], sh.part[3][1][row]));
         if (warp == 0) {
           // tiles of the next pass (all of them if nothing was marked: non-finite scores)
           const int lo_t = lane * 32;
@@ -831,7 +865,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             for (int w = 0; w * 32 < nkt; ++w) nact_pass += __popc(((volatile uint32_t*)sh.act[rpass & 1u])[w]);
             // (general alpha: no turns.  Its arithmetic is a long dependent chain per entry on a divergent path, and
             // four warps per scheduler hide that latency better than two.)
-            constexpr bool kTurns = KIND != 2;
+            constexpr bool kTurns = KIND != 2 && !PAIR;   // (two-tile form: both groups sum at once)
             if (kTurns && (uint32_t)grp != first_grp) named_bar_arrive(4 + (int)first_grp, kFwdRowThreads);
             for_my_tiles(rpass, [&](int kt, uint32_t cs) {
               const uint32_t buf = cs & 3;
@@ -911,9 +945,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             sh.part[quad][2][row] = a2 + b2;
             named_bar_sync(1, kFwdRowThreads);
             if (!done) {
-              const float sum0 = (sh.part[0][0][row] + sh.part[1][0][row]) + (sh.part[2][0][row] + sh.part[3][0][row]);
-              const float sum1 = (sh.part[0][1][row] + sh.part[1][1][row]) + (sh.part[2][1][row] + sh.part[3][1][row]);
-              const float sum2v = (sh.part[0][2][row] + sh.part[1][2][row]) + (sh.part[2][2][row] + sh.part[3][2][row]);
+              const float sum0 = PAIR ? sh.part[2 * grp][0][row] + sh.part[2 * grp + 1][0][row]
+                                      : (sh.part[0][0][row] + sh.part[1][0][row]) + (sh.part[2][0][row] + sh.part[3][0][row]);
+              const float sum1 = PAIR ? sh.part[2 * grp][1][row] + sh.part[2 * grp + 1][1][row]
+                                      : (sh.part[0][1][row] + sh.part[1][1][row]) + (sh.part[2][1][row] + sh.part[3][1][row]);
+              const float sum2v = PAIR ? sh.part[2 * grp][2][row] + sh.part[2 * grp + 1][2][row]
+                                       : (sh.part[0][2][row] + sh.part[1][2][row]) + (sh.part[2][2][row] + sh.part[3][2][row]);
               // Tile skipping relies on tau not falling.  A fall within rounding is dropped; a real
               // one (after a first step that overshot, or a bisection) makes the next pass visit the
               // tiles of the first threshold pass again: tau never leaves the bracket, whose lower
@@ -1031,24 +1068,45 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         rpass = 1;
       }
 
+      // ---- last pass(es) ---------------------------------------------------------------------------
+      // Two-tile form: one run per live query tile; all sixteen row warps work on that tile's rows as in the
+      // one-tile form (the two groups take alternate key tiles, two threads of a group share a row).
+      if (PAIR) {   // the thresholds of both query tiles, for the runs below (the partial-sum slots are free now)
+        named_bar_sync(1, kFwdRowThreads);
+        if (half == 0) sh.part[grp][0][row] = rstat;
+        named_bar_sync(1, kFwdRowThreads);
+      }
+      int nfin_rows = 0;
+      for (int w = 0; w * 32 < nkt; ++w) nfin_rows += __popc(((volatile uint32_t*)sh.act[rpass & 1u])[w]);
+      for (int sub = 0; sub < (PAIR ? nsub : 1); ++sub) {
+      const int row0_s = PAIR ? row0 + sub * 128 : row0g;
+      const int i_s = row0_s + row;
+      const bool live_s = i_s < len;
+      const int jlim_s = live_s ? (causal ? min(i_s, len - 1) : len - 1) : -1;
+      const int tile_jlim_s = (row0_s + 127 < len) ? (causal ? row0_s : len - 1) : -1;
+      const float rstat_s = PAIR ? sh.part[sub][0][row] : rstat;
+      const uint32_t use0 = (uint32_t)sub * (uint32_t)((nfin_rows + 1 - grp) >> 1);
       // ---- last pass: probabilities into tensor memory --------------------------------------
       // S(t) lands in score buffer t & 1; the probabilities go to a buffer of their own (64 columns
       // behind the output accumulator), so the next score product into the same score buffer
       // needs only these threads to have read it, not the P.V product to have finished.
       const float c1 = p.scale * (MODE == ENTMAX ? (p.alpha - 1.f) : kLog2e);
       const float e = MODE == ENTMAX ? 1.f / (p.alpha - 1.f) : 0.f;
-      const float tau_row = MODE == LAZY ? p.tau_h[h] / (float)(i + 1) : 0.f;
+      const float tau_row = MODE == LAZY ? p.tau_h[h] / (float)(i_s + 1) : 0.f;
       const uint32_t sbase = tgrp + grp * 128 + c0;                 // my half of score buffer grp
       const uint32_t pbase = tgrp + kProbCol + grp * 64 + half * 32;   // my half of probability buffer grp
-      sn = 0;
-      for_my_tiles(rpass, [&](int kt, uint32_t u) {
-        mbar_wait(&sh.f_full[grp], (u >> 1) & 1, abort_flag, status, 33);
-        // the P.V product two tiles back must have read the probability buffer
-        if (u >= 2) mbar_wait(&sh.pv_done[grp], ((u - 2) >> 1) & 1, abort_flag, status, 36);
+      uint32_t u_run = 0;
+      for_each_tile(rpass, [&](int kt) {
+        const uint32_t u = u_run++;
+        if ((u & 1u) != (uint32_t)grp) return;
+        const uint32_t use = use0 + (u >> 1);    // of the buffers of parity grp (they complete once per tile)
+        mbar_wait(&sh.f_full[grp], use & 1u, abort_flag, status, 33);
+        // the P.V product that last read this probability buffer must be done
+        if (use >= 1u) mbar_wait(&sh.pv_done[grp], (use - 1u) & 1u, abort_flag, status, 36);
         __syncwarp();
         tc_fence_after_sync();
-        const bool need_mask = kt * 128 + 127 > tile_jlim;
-        const int climit = jlim - kt * 128 - c0;
+        const bool need_mask = kt * 128 + 127 > tile_jlim_s;
+        const int climit = jlim_s - kt * 128 - c0;
         const bool in_window = MODE == LAZY && (row0 - kt * 128 - 127 < p.window);
         uint32_t nz = 0;
 #pragma unroll 1
@@ -1059,17 +1117,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             // alpha = 1.5, no masked entry: P = max(x, 0)^2 with the clamp folded into the fma
 #pragma unroll
             for (int x = 0; x < 32; x += 2) {
-              const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, -rstat));
-              const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, -rstat));
+              const float e0 = __saturatef(fmaf(__uint_as_float(r[x]), c1, -rstat_s));
+              const float e1 = __saturatef(fmaf(__uint_as_float(r[x + 1]), c1, -rstat_s));
               pk[x >> 1] = pack16<FMT>(e0 * e0, e1 * e1);
               nz |= pk[x >> 1];
             }
           } else if (MODE == LAZY && !need_mask && !in_window) {
-            // interior tile: A = max(exp2(x - lse) + tau_h/(i+1), 0), straight-line
+            // interior tile: A = max(exp2(x - lse) + tau_h/(i_s+1), 0), straight-line
 #pragma unroll
             for (int x = 0; x < 32; x += 2) {
-              const float t0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, -rstat)) + tau_row;
-              const float t1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, -rstat)) + tau_row;
+              const float t0 = fast_exp2(fmaf(__uint_as_float(r[x]), c1, -rstat_s)) + tau_row;
+              const float t1 = fast_exp2(fmaf(__uint_as_float(r[x + 1]), c1, -rstat_s)) + tau_row;
               pk[x >> 1] = pack16<FMT>(fmaxf(t0, 0.f), fmaxf(t1, 0.f));
               nz |= pk[x >> 1];
             }
@@ -1084,15 +1142,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 const bool valid = !need_mask || c <= climit;
                 float pw = 0.f;
                 if (MODE == ENTMAX) {
-                  const float d = fmaf(sc, c1, -rstat);
+                  const float d = fmaf(sc, c1, -rstat_s);
                   if (valid && d > 0.f) pw = pow_e<KIND>(d, e);
                 } else {
                   float v = sc * c1;
                   if (in_window) {
-                    const int dist = i - (kt * 128 + c0 + c);
+                    const int dist = i_s - (kt * 128 + c0 + c);
                     if (dist >= 0 && dist < p.window) v = fmaf(__ldg(p.bias + (int64_t)h * p.bias_stride + dist), kLog2e, v);
                   }
-                  const float t = fast_exp2(v - rstat) + tau_row;
+                  const float t = fast_exp2(v - rstat_s) + tau_row;
                   if (valid && t > 0.f) pw = t;
                 }
                 pv[y] = pw;
@@ -1117,43 +1175,71 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       });
 
       // ---- epilogue: each of the four threads of a row stores 32 output columns -----------------
-      mbar_wait(&sh.o_full, 0, abort_flag, status, 34);
+      mbar_wait(&sh.o_full, (uint32_t)sub & 1u, abort_flag, status, 34);
       __syncwarp();
       tc_fence_after_sync();
-      const bool in_range = i < L;
-      uint8_t* orow = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i * p.o.s[2]);
+      const bool in_range = i_s < L;
+      uint8_t* orow = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i_s * p.o.s[2]);
       if (quad < D / 32) {
         uint32_t r[32];
         tmem_ld32_sync(tmem_o + lane_base + quad * 32, r);
+        if (PAIR) {   // the accumulator may be overwritten by the next query tile's first product
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh.o_read);
+        }
         if (in_range) {
 #pragma unroll
           for (int x = 0; x < 32; x += 8) {
             uint4 w;
-            w.x = live ? pack16<FMT>(__uint_as_float(r[x]), __uint_as_float(r[x + 1])) : 0u;
-            w.y = live ? pack16<FMT>(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3])) : 0u;
-            w.z = live ? pack16<FMT>(__uint_as_float(r[x + 4]), __uint_as_float(r[x + 5])) : 0u;
-            w.w = live ? pack16<FMT>(__uint_as_float(r[x + 6]), __uint_as_float(r[x + 7])) : 0u;
+            w.x = live_s ? pack16<FMT>(__uint_as_float(r[x]), __uint_as_float(r[x + 1])) : 0u;
+            w.y = live_s ? pack16<FMT>(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3])) : 0u;
+            w.z = live_s ? pack16<FMT>(__uint_as_float(r[x + 4]), __uint_as_float(r[x + 5])) : 0u;
+            w.w = live_s ? pack16<FMT>(__uint_as_float(r[x + 6]), __uint_as_float(r[x + 7])) : 0u;
             *(uint4*)(orow + (quad * 32 + x) * 2) = w;
           }
         }
       }
       if (in_range && quad == 0) {
-        if (MODE == ENTMAX) p.tau[bhl + i] = live ? rstat : 0.f;
-        else p.lse[bhl + i] = live ? rstat : 0.f;
+        if (MODE == ENTMAX) p.tau[bhl + i_s] = live_s ? rstat_s : 0.f;
+        else p.lse[bhl + i_s] = live_s ? rstat_s : 0.f;
       }
+      if (PAIR && quad >= D / 32 && lane == 0) mbar_arrive(&sh.o_read);   // (warps without output columns)
       named_bar_sync(1, kFwdRowThreads);
-      if (MODE == ENTMAX && p.block_mask != nullptr && tid < p.mask_words)
-        p.block_mask[((int64_t)bh * nmt + mt) * p.mask_words + tid] = sh.mask_words[tid];
-    } else if (i < L) {
-      // the whole tile is padding: zeros
-      uint8_t* orow = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i * p.o.s[2]);
-      if (quad < D / 32) {
-#pragma unroll
-        for (int x = 0; x < 32; x += 8) *(uint4*)(orow + (quad * 32 + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
+      if (MODE == ENTMAX && p.block_mask != nullptr && tid < p.mask_words) {
+        p.block_mask[((int64_t)bh * nmt + mt + sub) * p.mask_words + tid] = sh.mask_words[tid];
+        if (PAIR) sh.mask_words[tid] = 0u;
       }
-      if (quad == 0) {
-        if (MODE == ENTMAX) p.tau[bhl + i] = 0.f;
-        else p.lse[bhl + i] = 0.f;
+      if (PAIR) named_bar_sync(1, kFwdRowThreads);
+      }   // per query tile
+      if (PAIR && nsub < 2) {
+        // the second query tile of the CTA is all padding (or beyond L): zeros, a quarter of a row per thread
+        const int i2 = row0 + 128 + row;
+        if (i2 < L) {
+          uint8_t* orow2 = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i2 * p.o.s[2]);
+          if (quad < D / 32) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 8) *(uint4*)(orow2 + (quad * 32 + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          if (quad == 0) p.tau[bhl + i2] = 0.f;
+        }
+      }
+    } else if (i < L) {
+      // the whole tile is padding: zeros (two-tile form: a row has the two threads of one group, half a row each)
+      uint8_t* orow = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i * p.o.s[2]);
+      if (PAIR) {
+#pragma unroll
+        for (int x = 0; x < D / 2; x += 8) *(uint4*)(orow + (half * (D / 2) + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
+        if (half == 0) p.tau[bhl + i] = 0.f;
+      } else {
+        if (quad < D / 32) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) *(uint4*)(orow + (quad * 32 + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (quad == 0) {
+          if (MODE == ENTMAX) p.tau[bhl + i] = 0.f;
+          else p.lse[bhl + i] = 0.f;
+        }
       }
     }
     tc_fence_before_sync();

@@ -53,6 +53,8 @@ extern "C" {
                                        * tail-model step                                         */
 #define FLA_FLAG_CANDIDATE_LIST 4     /* iterate the thresholds on kept candidates for every      *
                                        * alpha (the default does so for alpha = 2 only)          */
+#define FLA_FLAG_ONE_TILE_CTAS 8      /* entmax forward by score passes: one query tile per      *
+                                       * thread block (default: two, sharing every K tile fetch)  */
 
 /* A strided [B,H,L,D] view; strides in elements, stride[3] must be 1. */
 typedef struct fla_tensor4 {

@@ -42,7 +42,8 @@ def test_candidate_lists_and_score_passes_agree(alpha, causal, L, D):
         assert last_call_info()["path"] == "tcgen05" and st["error"] == 0
         res[name] = (out.float(), tau, mask, st)
     tiles = B * H * ((L + 127) // 128)
-    assert res["passes"][3]["pass_ctas"] == tiles and res["passes"][3]["list_ctas"] == 0
+    pairs = B * H * (((L + 127) // 128 + 1) // 2)    # the pass-only forward holds two query tiles per thread block
+    assert res["passes"][3]["pass_ctas"] == pairs and res["passes"][3]["list_ctas"] == 0
     assert res["lists"][3]["list_ctas"] + res["lists"][3]["pass_ctas"] == tiles
     if alpha >= 1.5:      # small supports: the candidates fit the slots and the spill pool
         assert res["lists"][3]["list_ctas"] == tiles, res["lists"][3]
@@ -51,6 +52,34 @@ def test_candidate_lists_and_score_passes_agree(alpha, causal, L, D):
     assert maxdiff(res["lists"][1], tau_ref) <= 2e-4, maxdiff(res["lists"][1], tau_ref)
     assert maxdiff(res["passes"][1], tau_ref) <= 5e-4, maxdiff(res["passes"][1], tau_ref)
     assert maxdiff(res["lists"][0], res["passes"][0]) <= 2e-2
+
+
+@pytest.mark.parametrize("alpha", [1.5, 1.333])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("L,D,lens", [(700, 128, None), (1409, 64, [1409, 130]), (128, 128, None), (2048, 128, [1000, 2048])])
+def test_two_query_tiles_per_block_equal_one(alpha, causal, L, D, lens):
+    """The pass-only forward with two query tiles per thread block (sharing every K tile it fetches) against the
+    one-tile form: the same arithmetic per entry, the row sums added up in a different order (two threads per row
+    taking every key tile, instead of four taking alternate ones) -- thresholds within 2e-5, outputs within one
+    16-bit unit, block masks equal up to entries sitting on a threshold.  Odd tile counts, a second tile that is
+    all padding, a single tile."""
+    B, H, dtype = (1 if lens is None else len(lens)), 2, torch.bfloat16
+    q, k, v = (randn((B, H, L, D), dtype, s) for s in (1, 2, 3))
+    varlen = None if lens is None else torch.tensor(lens, device="cuda")
+    res = []
+    for flags in (_lib.FLAG_NO_CANDIDATE_LIST, _lib.FLAG_NO_CANDIDATE_LIST | _lib.FLAG_ONE_TILE_CTAS):
+        set_flags(flags)
+        out, tau, _, _, mask = entmax_attention_forward(q, k, v, alpha, 10, causal, varlen, use_block_mask=True)
+        assert last_call_info()["path"] == "tcgen05"
+        res.append((out, tau, mask))
+    (o2, t2, m2), (o1, t1, m1) = res
+    assert maxdiff(t2, t1) <= 2e-5, maxdiff(t2, t1)
+    assert maxdiff(o2, o1) <= 2.0 ** -7 * max(1.0, float(o1.float().abs().max())), maxdiff(o2, o1)
+    differing = int(((m2 ^ m1) != 0).sum())
+    assert differing <= max(1, m1.numel() // 500), differing
+    if lens is not None:
+        for b_, n in enumerate(lens):
+            assert (o2[b_, :, n:] == 0).all() and (t2[b_, :, n:] == 0).all()
 
 
 def test_list_overflow_falls_back_to_score_passes():
