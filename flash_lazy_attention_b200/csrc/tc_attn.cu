@@ -36,7 +36,7 @@ bool view_ok(const View4& v, const char** why) {
 template <int MODE, int D, bool LISTS, bool PAIR>
 constexpr size_t fwd_smem_bytes() {   // the query tile(s), the K/V ring; with kept candidates: their staging slots
   return (size_t)tc::TileCfg<D>::kTileBytes * ((PAIR ? 2 : 1) + tc::TileCfg<D>::kStages) + 1024 +
-         ((MODE == ENTMAX && !PAIR) ? tc::kStageBytes : 0);
+         (PAIR ? 4 * tc::kMaxMaskWords : (MODE == ENTMAX ? tc::kStageBytes : 0));   // two-tile form: its second mask row
 }
 
 template <int MODE, int D, int FMT, int KIND, bool LISTS, bool PAIR = false>

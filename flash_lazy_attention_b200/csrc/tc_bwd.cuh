@@ -88,21 +88,6 @@ __device__ __forceinline__ void prob_terms(float x, float e, float tau_row, bool
 }
 
 
-// D[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory as four pieces of 16 columns (16-bit
-// pairs), piece q at a_tmem + 32 q (each of the four threads of a row writes its 32 reduction elements inside
-// the columns it read); B a [128 rows x D] tile whose rows are the reduction dimension.  `nks`: 16-row steps
-// to issue (fewer than 8 for the tile that reaches into a sequence's padding).
-template <int D, int FMT>
-__device__ __forceinline__ void issue_tn_quads(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
-                                               int nks = 8) {
-  constexpr uint32_t idesc = make_idesc(128, D, FMT, 0, 1);
-#pragma unroll
-  for (int ks = 0; ks < 8; ++ks)
-    if (ks < nks)
-      umma_ts(d_tmem, a_tmem + 32 * (ks >> 1) + 8 * (ks & 1), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
-              (accumulate || ks > 0) ? 1u : 0u);
-}
-
 // ------------------------------------------------------------------------------------------------
 // Warps 0-15: row threads, four per query row (thread q of a row takes keys [32q, 32q+32) of every
 // tile: sixteen warps keep the schedulers busy while others wait for a product, and the single S buffer of the

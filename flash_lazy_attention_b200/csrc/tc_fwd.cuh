@@ -59,7 +59,7 @@ struct TileCfg {
 };
 
 struct FwdShared {
-  uint64_t q_full, ring_full[8], ring_empty[8], s_full[4], s_free[4], f_full[2], p_full[2], pv_done[2], pass_done, o_full, o_read;
+  uint64_t q_full, ring_full[8], ring_empty[8], s_full[4], s_free[4], f_full[2], p_full[2], pv_done[2], pass_done, o_full;
   uint32_t tmem_base;
   int abort_flag;
   int cont_flag;
@@ -125,6 +125,21 @@ __device__ __forceinline__ void issue_tn(uint32_t d_tmem, uint32_t a_tmem, uint3
   for (int ks = 0; ks < 8; ++ks)
     if (ks < nks)
       umma_ts(d_tmem, a_tmem + ks * 8, desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
+              (accumulate || ks > 0) ? 1u : 0u);
+}
+
+// D[128 x D] (+)= A[128 x 128] . B[128 x D]: A in tensor memory as four pieces of 16 columns (16-bit
+// pairs), piece q at a_tmem + 32 q (each of the four threads of a row writes its 32 reduction elements inside
+// the columns it read); B a [128 rows x D] tile whose rows are the reduction dimension.  `nks`: 16-row steps
+// to issue (fewer than 8 for the tile that reaches into a sequence's padding).
+template <int D, int FMT>
+__device__ __forceinline__ void issue_tn_quads(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool accumulate,
+                                               int nks = 8) {
+  constexpr uint32_t idesc = make_idesc(128, D, FMT, 0, 1);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    if (ks < nks)
+      umma_ts(d_tmem, a_tmem + 32 * (ks >> 1) + 8 * (ks & 1), desc_mnmajor(b_addr + ks * 2048, TileCfg<D>::kBoxBytes), idesc,
               (accumulate || ks > 0) ? 1u : 0u);
 }
 
@@ -304,13 +319,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     }
     mbar_init(&sh.pass_done, 1);
     mbar_init(&sh.pass_ack, 3);
-    mbar_init(&sh.o_full, 1);
-    mbar_init(&sh.o_read, kFwdRowThreads / 32);
+    mbar_init(&sh.o_full, PAIR ? 2 : 1);   // (two-tile form: one commit per issuer)
     sh.abort_flag = 0;
     sh.cont_flag = 0;
     fence_mbar_init();
   }
-  if (tid < kMaxMaskWords) sh.mask_words[tid] = 0;
+  if (tid < kMaxMaskWords) {
+    sh.mask_words[tid] = 0;
+    if (PAIR) reinterpret_cast<uint32_t*>(stage)[tid] = 0;   // (block-mask words of the second query tile)
+  }
   if (tid < kFwdRowThreads) {
     (&sh.rmax[0][0])[tid] = -INFINITY;
     (&sh.rlb[0][0])[tid] = -INFINITY;
@@ -398,7 +415,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         mbar_arrive(&sh.pass_ack);
         if (!go_on || *abort_flag) break;
       }
-      for (int sub = 0; sub < nsub; ++sub) {   // last pass (per query tile): K(0), K(1), V(0), K(2), V(1), ..., V(n-1)
+      {   // last pass: K(0), K(1), V(0), K(2), V(1), ..., V(n-1)
         int prev = -1;
         for_each_tile(pass, [&](int kt) {
           load(&map_k, kt, 12);
@@ -461,41 +478,59 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       const int tail_valid = len - (nkt - 1) * 128;
       const bool tail_visited = nkt > 0 && tail_valid < 128 &&
                                 ((((volatile uint32_t*)sh.act[pass & 1u])[(nkt - 1) >> 5] >> ((nkt - 1) & 31)) & 1u) != 0u;
-      // Two-tile form: the pass runs once per live query tile.  The barriers of buffer sb (f_full, p_full, pv_done)
-      // complete once per tile of parity sb, so tile t of run `sub` is use number sub * ceil or floor(nfin / 2) +
-      // t / 2 of its buffer, and the ring goes on from where the previous run left it.
-      for (int sub = 0; sub < (PAIR ? nsub : 1); ++sub) {
-        const uint32_t q_sub = q_addr + (uint32_t)sub * Cfg::kTileBytes;
+      if constexpr (PAIR) {
+        // Two-tile form: both query tiles go through the last pass together, on the same K and V tiles.  Issuer g
+        // serves query tile g: S_g(t) into score buffer g, then -- once row group g has written P_g(t) over it --
+        // O_g += P_g(t) . V(t), accumulators at columns 256 and 384.  A K or V slot is released by the commits of
+        // both issuers.  The chain S -> P -> P.V -> next S of one query tile runs while the other tile's does.
+        const uint32_t q_mine = q_addr + me * Cfg::kTileBytes, s_mine = tmem + me * 128, o_mine = tmem + 256 + me * 128;
+        for (int t = 0; t < nfin; ++t) {
+          const uint32_t ok_ofs = fin_k_ofs(t), ov_ofs = fin_v_ofs(t, nfin);
+          const uint32_t stk = rp.stage_at(ok_ofs), stv = rp.stage_at(ov_ofs);
+          bool ok = mbar_wait(&sh.ring_full[stk], rp.phase_at(ok_ofs), abort_flag, status, 24 + me);
+          // P_g(t-1) stands in this buffer until its product has read it
+          if (t >= 1) ok = ok && mbar_wait(&sh.pv_done[me], (uint32_t)(t - 1) & 1u, abort_flag, status, 28);
+          tc_fence_after_sync();
+          if (ok) issue_nt<D, FMT>(s_mine, q_mine, ring_addr + stk * Cfg::kTileBytes);
+          umma_commit(&sh.ring_empty[stk]);
+          umma_commit(&sh.f_full[me]);
+          ok = ok && mbar_wait(&sh.p_full[me], (uint32_t)t & 1u, abort_flag, status, 26);
+          ok = ok && mbar_wait(&sh.ring_full[stv], rp.phase_at(ov_ofs), abort_flag, status, 24 + me);
+          tc_fence_after_sync();
+          int nks = 8;
+          // (both issuers clear the same padding rows with the same zeros)
+          if (ok && tail_visited && t == nfin - 1) nks = zero_tail_rows(ring + stv * Cfg::kTileBytes, tail_valid, Cfg::kBoxes, 128);
+          if (ok) issue_tn_quads<D, FMT>(o_mine, s_mine, ring_addr + stv * Cfg::kTileBytes, t > 0, nks);
+          umma_commit(&sh.ring_empty[stv]);
+          umma_commit(&sh.pv_done[me]);
+          issued += 2;
+        }
+        umma_commit(&sh.o_full);
+      } else {
         for (int t = 0; t < nfin; ++t) {
           const uint32_t sb = (uint32_t)t & 1u;
-          const uint32_t use = (uint32_t)sub * (uint32_t)((nfin + 1 - (int)sb) >> 1) + ((uint32_t)t >> 1);   // of buffer sb
           const uint32_t ofs = score_role ? fin_k_ofs(t) : fin_v_ofs(t, nfin);
           const uint32_t st = rp.stage_at(ofs);
           bool ok = mbar_wait(&sh.ring_full[st], rp.phase_at(ofs), abort_flag, status, 24 + me);
           if (score_role) {
-            // the row threads have read the previous S out of this buffer (their probabilities live elsewhere)
-            if (use >= 1u) ok = ok && mbar_wait(&sh.p_full[sb], (use - 1u) & 1u, abort_flag, status, 28);
+            // the row threads have read S(t-2) out of this buffer (their probabilities live elsewhere)
+            if (t >= 2) ok = ok && mbar_wait(&sh.p_full[sb], ((t - 2) >> 1) & 1, abort_flag, status, 28);
             tc_fence_after_sync();
-            if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_sub, ring_addr + st * Cfg::kTileBytes);
+            if (ok) issue_nt<D, FMT>(tmem + sb * 128, q_addr, ring_addr + st * Cfg::kTileBytes);
             umma_commit(&sh.ring_empty[st]);
-            if (PAIR) umma_commit(&sh.ring_empty[st]);
             umma_commit(&sh.f_full[sb]);
           } else {
-            ok = ok && mbar_wait(&sh.p_full[sb], use & 1u, abort_flag, status, 26);
-            // the output accumulator of the previous query tile has been read out before it is overwritten
-            if (PAIR && sub > 0 && t == 0) ok = ok && mbar_wait(&sh.o_read, (uint32_t)(sub - 1) & 1u, abort_flag, status, 27);
+            ok = ok && mbar_wait(&sh.p_full[sb], (t >> 1) & 1, abort_flag, status, 26);
             tc_fence_after_sync();
             int nks = 8;
             if (ok && tail_visited && t == nfin - 1) nks = zero_tail_rows(ring + st * Cfg::kTileBytes, tail_valid, Cfg::kBoxes, 128);
             if (ok) issue_tn<D, FMT, FMT>(tmem_o, tmem + kProbCol + sb * 64, ring_addr + st * Cfg::kTileBytes, t > 0, nks);
             umma_commit(&sh.ring_empty[st]);
-            if (PAIR) umma_commit(&sh.ring_empty[st]);
             umma_commit(&sh.pv_done[sb]);
           }
           ++issued;
         }
         if (!score_role) umma_commit(&sh.o_full);
-        rp.pos += 2u * (uint32_t)nfin;
       }
       if (status) atomicAdd((unsigned long long*)(status + 4), issued);
     }
@@ -1068,24 +1103,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         rpass = 1;
       }
 
-      // ---- last pass(es) ---------------------------------------------------------------------------
-      // Two-tile form: one run per live query tile; all sixteen row warps work on that tile's rows as in the
-      // one-tile form (the two groups take alternate key tiles, two threads of a group share a row).
-      if (PAIR) {   // the thresholds of both query tiles, for the runs below (the partial-sum slots are free now)
-        named_bar_sync(1, kFwdRowThreads);
-        if (half == 0) sh.part[grp][0][row] = rstat;
-        named_bar_sync(1, kFwdRowThreads);
-      }
-      int nfin_rows = 0;
-      for (int w = 0; w * 32 < nkt; ++w) nfin_rows += __popc(((volatile uint32_t*)sh.act[rpass & 1u])[w]);
-      for (int sub = 0; sub < (PAIR ? nsub : 1); ++sub) {
-      const int row0_s = PAIR ? row0 + sub * 128 : row0g;
-      const int i_s = row0_s + row;
-      const bool live_s = i_s < len;
-      const int jlim_s = live_s ? (causal ? min(i_s, len - 1) : len - 1) : -1;
-      const int tile_jlim_s = (row0_s + 127 < len) ? (causal ? row0_s : len - 1) : -1;
-      const float rstat_s = PAIR ? sh.part[sub][0][row] : rstat;
-      const uint32_t use0 = (uint32_t)sub * (uint32_t)((nfin_rows + 1 - grp) >> 1);
+      // ---- last pass ------------------------------------------------------------------------------
+      // One-tile form: the two groups take alternate key tiles of the one query tile.  Two-tile form: group g works
+      // on its own query tile for every key tile and writes the probabilities over the scores it read them from
+      // (score buffer g; accumulator g), see the issuers.
+      {
+      constexpr int sub = 0;
+      const int i_s = i;
+      const bool live_s = live;
+      const int jlim_s = jlim;
+      const int tile_jlim_s = tile_jlim;
+      const float rstat_s = rstat;
+      const uint32_t use0 = 0;
+      uint32_t* const my_mask = PAIR && grp == 1 ? reinterpret_cast<uint32_t*>(stage) : sh.mask_words;   // (two-tile form: the second
+                                                                  // tile's block-mask words live behind the ring)
       // ---- last pass: probabilities into tensor memory --------------------------------------
       // S(t) lands in score buffer t & 1; the probabilities go to a buffer of their own (64 columns
       // behind the output accumulator), so the next score product into the same score buffer
@@ -1098,11 +1129,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       uint32_t u_run = 0;
       for_each_tile(rpass, [&](int kt) {
         const uint32_t u = u_run++;
-        if ((u & 1u) != (uint32_t)grp) return;
-        const uint32_t use = use0 + (u >> 1);    // of the buffers of parity grp (they complete once per tile)
+        if (!PAIR && (u & 1u) != (uint32_t)grp) return;
+        const uint32_t use = PAIR ? u : use0 + (u >> 1);    // of the buffers of this group (they complete once per tile of its)
         mbar_wait(&sh.f_full[grp], use & 1u, abort_flag, status, 33);
-        // the P.V product that last read this probability buffer must be done
-        if (use >= 1u) mbar_wait(&sh.pv_done[grp], (use - 1u) & 1u, abort_flag, status, 36);
+        // the P.V product that last read this probability buffer must be done (two-tile form: the score product
+        // waited for it already)
+        if (!PAIR && use >= 1u) mbar_wait(&sh.pv_done[grp], (use - 1u) & 1u, abort_flag, status, 36);
         __syncwarp();
         tc_fence_after_sync();
         const bool need_mask = kt * 128 + 127 > tile_jlim_s;
@@ -1159,7 +1191,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               nz |= pk[x >> 1];
             }
           }
-          tmem_st16(pbase + ch * 16, pk);
+          tmem_st16(PAIR ? sbase + ch * 32 : pbase + ch * 16, pk);
         }
         tmem_st_wait();
         tc_fence_before_sync();
@@ -1169,25 +1201,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           // key block (64 keys) 2 kt + half holds a non-zero probability for some row of this warp
           if (__any_sync(0xffffffffu, nz != 0) && lane == 0) {
             const int j = 2 * kt + half;
-            atomicOr(&sh.mask_words[j >> 5], 1u << (j & 31));
+            atomicOr(&my_mask[j >> 5], 1u << (j & 31));
           }
         }
       });
 
-      // ---- epilogue: each of the four threads of a row stores 32 output columns -----------------
-      mbar_wait(&sh.o_full, (uint32_t)sub & 1u, abort_flag, status, 34);
+      // ---- epilogue: each of the four (two-tile form: two) threads of a row stores its share of the output columns
+      mbar_wait(&sh.o_full, 0, abort_flag, status, 34);
       __syncwarp();
       tc_fence_after_sync();
       const bool in_range = i_s < L;
       uint8_t* orow = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i_s * p.o.s[2]);
-      if (quad < D / 32) {
+      // columns [col0, col0 + 32 nld) of the accumulator: a quarter of the row, or half of it
+      const int nld = PAIR ? D / 64 : (quad < D / 32 ? 1 : 0);
+      const int col0 = PAIR ? half * (D / 2) : quad * 32;
+      const uint32_t acc = PAIR ? tmem + 256 + grp * 128 : tmem_o;
+      for (int part = 0; part < nld; ++part) {
         uint32_t r[32];
-        tmem_ld32_sync(tmem_o + lane_base + quad * 32, r);
-        if (PAIR) {   // the accumulator may be overwritten by the next query tile's first product
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sh.o_read);
-        }
+        tmem_ld32_sync(acc + lane_base + col0 + part * 32, r);
         if (in_range) {
 #pragma unroll
           for (int x = 0; x < 32; x += 8) {
@@ -1196,33 +1227,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             w.y = live_s ? pack16<FMT>(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3])) : 0u;
             w.z = live_s ? pack16<FMT>(__uint_as_float(r[x + 4]), __uint_as_float(r[x + 5])) : 0u;
             w.w = live_s ? pack16<FMT>(__uint_as_float(r[x + 6]), __uint_as_float(r[x + 7])) : 0u;
-            *(uint4*)(orow + (quad * 32 + x) * 2) = w;
+            *(uint4*)(orow + (col0 + part * 32 + x) * 2) = w;
           }
         }
       }
-      if (in_range && quad == 0) {
+      if (in_range && (PAIR ? half == 0 : quad == 0)) {
         if (MODE == ENTMAX) p.tau[bhl + i_s] = live_s ? rstat_s : 0.f;
         else p.lse[bhl + i_s] = live_s ? rstat_s : 0.f;
       }
-      if (PAIR && quad >= D / 32 && lane == 0) mbar_arrive(&sh.o_read);   // (warps without output columns)
       named_bar_sync(1, kFwdRowThreads);
       if (MODE == ENTMAX && p.block_mask != nullptr && tid < p.mask_words) {
         p.block_mask[((int64_t)bh * nmt + mt + sub) * p.mask_words + tid] = sh.mask_words[tid];
-        if (PAIR) sh.mask_words[tid] = 0u;
+        if (PAIR && mt + 1 < nmt)
+          p.block_mask[((int64_t)bh * nmt + mt + 1) * p.mask_words + tid] = reinterpret_cast<uint32_t*>(stage)[tid];
       }
-      if (PAIR) named_bar_sync(1, kFwdRowThreads);
-      }   // per query tile
-      if (PAIR && nsub < 2) {
-        // the second query tile of the CTA is all padding (or beyond L): zeros, a quarter of a row per thread
-        const int i2 = row0 + 128 + row;
-        if (i2 < L) {
-          uint8_t* orow2 = (uint8_t*)p.o.ptr + 2 * ((int64_t)b * p.o.s[0] + (int64_t)h * p.o.s[1] + (int64_t)i2 * p.o.s[2]);
-          if (quad < D / 32) {
-#pragma unroll
-            for (int x = 0; x < 32; x += 8) *(uint4*)(orow2 + (quad * 32 + x) * 2) = make_uint4(0u, 0u, 0u, 0u);
-          }
-          if (quad == 0) p.tau[bhl + i2] = 0.f;
-        }
       }
     } else if (i < L) {
       // the whole tile is padding: zeros (two-tile form: a row has the two threads of one group, half a row each)
