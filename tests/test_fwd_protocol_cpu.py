@@ -14,6 +14,13 @@ order per issuing thread.  A random scheduler interleaves everything.  The model
 With an odd ring depth and the issuers on alternate tiles the model fails (that configuration once
 faulted on the device); the kernel's even depths pass.  The second test checks the arrival counts
 of the named-barrier turn taking between the two row groups.
+
+The model is of the form with one query tile per thread block (Lazy Attention, the candidate-list
+solver, FLA_FLAG_ONE_TILE_CTAS).  The form with two query tiles per block runs the same slot and
+phase arithmetic on the running tile index 2t + g (g the issuer / row group, which owns query tile
+g), so that a tile sequence of this model with the two issuers on alternate tiles is the sequence
+that form executes; its last pass has one independent S -> P -> O chain per issuer and is covered on
+the device by tests/test_entmax_paths_gpu.py::test_two_query_tiles_per_block_equal_one.
 """
 import random
 
