@@ -15,12 +15,11 @@ With an odd ring depth and the issuers on alternate tiles the model fails (that 
 faulted on the device); the kernel's even depths pass.  The second test checks the arrival counts
 of the named-barrier turn taking between the two row groups.
 
-The model is of the form with one query tile per thread block (Lazy Attention, the candidate-list
-solver, FLA_FLAG_ONE_TILE_CTAS).  The form with two query tiles per block runs the same slot and
-phase arithmetic on the running tile index 2t + g (g the issuer / row group, which owns query tile
-g), so that a tile sequence of this model with the two issuers on alternate tiles is the sequence
-that form executes; its last pass has one independent S -> P -> O chain per issuer and is covered on
-the device by tests/test_entmax_paths_gpu.py::test_two_query_tiles_per_block_equal_one.
+Both forms of the kernel are modelled: one query tile per thread block (Lazy Attention, the
+candidate-list solver, FLA_FLAG_ONE_TILE_CTAS) and two (pair=True: issuer and row group g own query
+tile g and work on every key tile, with the running tile index 2t + g in the slot and phase
+arithmetic; a ring slot is released by both issuers; in the last pass each issuer runs its own
+S -> P -> P.V chain with the probabilities written over the scores).
 """
 import random
 
@@ -35,15 +34,23 @@ class Bar:
         if s.pending == 0: s.phase += 1; s.pending = s.count
     def done(s, parity): return (s.phase & 1) != parity
 
-def run(nkt, actives, seed, stages=4, verbose=False):
+def run(nkt, actives, seed, stages=4, verbose=False, pair=False):
     # actives: list of tile lists, one per score pass (pass 0 = all), plus the last pass's list
+    # pair: the form with two query tiles per thread block (issuer / row group g owns query tile g)
     rnd = random.Random(seed)
     npass = len(actives) - 1            # score passes
-    B = dict(ring_full=[Bar(2) for _ in range(stages)], ring_empty=[Bar(1) for _ in range(stages)],
+    nuse = 2 if pair else 1             # issuers that read a ring slot before it is released
+    B = dict(ring_full=[Bar(2) for _ in range(stages)], ring_empty=[Bar(nuse) for _ in range(stages)],
              s_full=[Bar(1) for _ in range(4)], s_free=[Bar(1) for _ in range(4)],
              f_full=[Bar(1) for _ in range(2)], p_full=[Bar(1) for _ in range(2)], pv_done=[Bar(1) for _ in range(2)],
-             pass_done=Bar(1), pass_ack=Bar(3), o_full=Bar(1), grp=Bar(2))
-    state = dict(cont=None, ring=[None] * stages, sbuf=[None] * 4, P=[None] * 2, o=[])
+             pass_done=Bar(1), pass_ack=Bar(3), o_full=Bar(nuse), grp=Bar(2))
+    state = dict(cont=None, ring=[None] * stages, sbuf=[None] * 4, P=[None] * 2, o=[], o2=([], []),
+                 readers=[0] * stages)
+    def release(st):
+        # a slot's content is gone once every issuer that reads it has done so
+        state["readers"][st] += 1
+        if state["readers"][st] == nuse:
+            state["readers"][st] = 0; state["ring"][st] = None
     events = []   # async completions: (fn)
     log = []
     def adv(rp):
@@ -86,14 +93,15 @@ def run(nkt, actives, seed, stages=4, verbose=False):
         issuer_queues[me] = queue
         while True:
             for kt in actives[ps]:
-                if (sn & 1) == me:
-                    sb = sn & 3
+                if pair or (sn & 1) == me:
+                    vs = 2 * sn + me if pair else sn
+                    sb = vs & 3
                     yield ("wait", B["ring_full"][rp[0]], rp[1], f"iss{me} ring_full")
-                    yield ("wait", B["s_free"][sb], ((sn >> 2) & 1) ^ 1, f"iss{me} s_free")
+                    yield ("wait", B["s_free"][sb], ((vs >> 2) & 1) ^ 1, f"iss{me} s_free")
                     st = rp[0]
                     assert state["ring"][st] == ("K", ps, kt), ("wrong ring content", state["ring"][st], ps, kt)
                     def done(st=st, sb=sb, tag=(ps, kt)):
-                        state["sbuf"][sb] = tag; state["ring"][st] = None
+                        state["sbuf"][sb] = tag; release(st)
                         B["ring_empty"][st].arrive(); B["s_full"][sb].arrive()
                     commit(done)
                 adv(rp); sn += 1
@@ -107,6 +115,31 @@ def run(nkt, actives, seed, stages=4, verbose=False):
         s_role = (sn & 1) == me
         pos0 = sn      # tiles that went through the ring so far (one slot per tile in the score passes)
         nf = len(fin)
+        if pair:
+            # issuer `me` runs the chain S -> P -> P.V of query tile `me`: score buffer `me`, accumulator `me`
+            for t, kt in enumerate(fin):
+                k_ofs = 0 if t == 0 else 2 * t - 1
+                v_ofs = 2 * nf - 1 if t == nf - 1 else 2 * t + 2
+                stk = (pos0 + k_ofs) % stages; phk = ((pos0 + k_ofs) // stages) & 1
+                stv = (pos0 + v_ofs) % stages; phv = ((pos0 + v_ofs) // stages) & 1
+                yield ("wait", B["ring_full"][stk], phk, f"iss{me} fin K ring_full")
+                if t >= 1: yield ("wait", B["pv_done"][me], (t - 1) & 1, f"iss{me} pv_done")
+                assert state["ring"][stk] == ("K", "fin", kt), ("fin wrong K", state["ring"][stk], kt)
+                assert t == 0 or state["o2"][me][-1:] == [fin[t - 1]], "S over P before P.V read it"
+                def done_s(st=stk, kt=kt):
+                    state["sbuf"][me] = ("fin", kt); release(st)
+                    B["ring_empty"][st].arrive(); B["f_full"][me].arrive()
+                commit(done_s)
+                yield ("wait", B["p_full"][me], t & 1, f"iss{me} p_full")
+                yield ("wait", B["ring_full"][stv], phv, f"iss{me} fin V ring_full")
+                assert state["ring"][stv] == ("V", "fin", kt), ("fin wrong V", state["ring"][stv], kt)
+                assert state["P"][me] == kt, ("wrong P", state["P"][me], kt)
+                def done_pv(st=stv, kt=kt):
+                    state["o2"][me].append(kt); release(st)
+                    B["ring_empty"][st].arrive(); B["pv_done"][me].arrive()
+                commit(done_pv)
+            commit(lambda: B["o_full"].arrive())
+            return
         for t, kt in enumerate(fin):
             sb = t & 1
             ofs = (0 if t == 0 else 2 * t - 1) if s_role else (2 * nf - 1 if t == nf - 1 else 2 * t + 2)
@@ -116,7 +149,7 @@ def run(nkt, actives, seed, stages=4, verbose=False):
                 if t >= 2: yield ("wait", B["p_full"][sb], ((t - 2) >> 1) & 1, "issS p_full")
                 assert state["ring"][st] == ("K", "fin", kt), ("fin wrong K", state["ring"][st], kt)
                 def done(st=st, sb=sb, kt=kt):
-                    state["sbuf"][sb] = ("fin", kt); state["ring"][st] = None
+                    state["sbuf"][sb] = ("fin", kt); release(st)
                     B["ring_empty"][st].arrive(); B["f_full"][sb].arrive()
                 commit(done)
             else:
@@ -124,7 +157,7 @@ def run(nkt, actives, seed, stages=4, verbose=False):
                 assert state["ring"][st] == ("V", "fin", kt), ("fin wrong V", state["ring"][st], kt)
                 assert state["P"][sb] == kt, ("wrong P", state["P"][sb], kt)
                 def done(st=st, sb=sb, kt=kt):
-                    state["o"].append(kt); state["ring"][st] = None
+                    state["o"].append(kt); release(st)
                     B["ring_empty"][st].arrive(); B["pv_done"][sb].arrive()
                 commit(done)
         if not s_role: commit(lambda: B["o_full"].arrive())
@@ -135,7 +168,8 @@ def run(nkt, actives, seed, stages=4, verbose=False):
             run_i = sn
             for kt in actives[ps]:
                 cs = run_i; run_i += 1
-                if (cs & 1) != g: continue
+                if pair: cs = 2 * cs + g      # every tile, for this group's query tile
+                elif (cs & 1) != g: continue
                 buf = cs & 3
                 yield ("wait", B["s_full"][buf], (cs >> 2) & 1, f"rows{g} s_full")
                 assert state["sbuf"][buf] == (ps, kt), ("rows read wrong buffer", state["sbuf"][buf], ps, kt)
@@ -151,6 +185,16 @@ def run(nkt, actives, seed, stages=4, verbose=False):
                 state["cont"] = ps + 1 < npass
                 B["pass_done"].arrive()
         fin = actives[npass]
+        if pair:
+            for u, kt in enumerate(fin):
+                yield ("wait", B["f_full"][g], u & 1, f"rows{g} f_full")
+                assert state["sbuf"][g] == ("fin", kt), ("rows fin wrong", state["sbuf"][g], kt)
+                state["sbuf"][g] = None          # the probabilities go over the scores
+                state["P"][g] = kt
+                B["p_full"][g].arrive()
+            yield ("wait", B["o_full"], 0, f"rows{g} o_full")
+            assert state["o2"][g] == fin, ("O order", g, state["o2"][g], fin)
+            return
         for u, kt in enumerate(fin):
             if (u & 1) != g: continue
             yield ("wait", B["f_full"][g], (u >> 1) & 1, f"rows{g} f_full")
@@ -216,6 +260,15 @@ def test_forward_protocol_has_no_deadlock_or_stale_operand(stages):
     rnd = random.Random(stages)
     for trial, (nkt, acts) in enumerate(_cases(rnd, 1500)):
         assert run(nkt, acts, trial, stages=stages) is None, (nkt, acts)
+
+
+@pytest.mark.parametrize("stages", [4, 8])
+def test_two_tile_form_has_no_deadlock_or_stale_operand(stages):
+    """Two query tiles per block: a ring slot is read by both issuers, each issuer and row group runs its own
+    S -> P -> P.V chain in the last pass, the output barrier takes one arrival per issuer."""
+    rnd = random.Random(100 + stages)
+    for trial, (nkt, acts) in enumerate(_cases(rnd, 1500)):
+        assert run(nkt, acts, trial, stages=stages, pair=True) is None, (nkt, acts)
 
 
 def test_odd_ring_depth_is_caught_by_the_model():
