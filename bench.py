@@ -319,6 +319,10 @@ def main():
     ap.add_argument("--flags", type=int, default=0,
                     help="fla_attn_geom.flags for the run (include/fla.h: 1 thresholds by passes over recomputed scores, "
                          "4 by candidates kept in the row-max pass; 0 = the library's choice)")
+    ap.add_argument("--niter", type=int, default=10,
+                    help="entmax workloads: cap on the threshold iterations (the metric is defined at the default, 10; "
+                         "0, 1, 2 ... time the forward with that many threshold passes and leave the thresholds "
+                         "unconverged: for the per-pass breakdown under profiles/ only)")
     ap.add_argument("--partition", action="store_true",
                     help="strong scaling: ONE seeded problem of the workload's size, its (batch, head) pairs split over "
                          "the ranks (no collective in the timed region); afterwards the ranks' results are gathered "
@@ -423,7 +427,7 @@ def main():
     def forward():
         if is_lazy:
             return fla.lazy_attention_triton(q, k, v, bias.to(q.dtype), tau_p.to(q.dtype), window_size=512)
-        return fla.adasplash(q, k, v, alpha=alpha, niter=10, is_causal=causal, varlen=varlen)
+        return fla.adasplash(q, k, v, alpha=alpha, niter=args.niter, is_causal=causal, varlen=varlen)
 
     def step():
         q.grad = k.grad = v.grad = None
@@ -491,7 +495,7 @@ def main():
                     sub = allp[c0:c0 + chunk]
                     fq, fk, fv, fdo = make_pairs(sub)
                     fq.requires_grad_(True), fk.requires_grad_(True), fv.requires_grad_(True)
-                    fo = fla.adasplash(fq, fk, fv, alpha=alpha, niter=10, is_causal=causal)
+                    fo = fla.adasplash(fq, fk, fv, alpha=alpha, niter=args.niter, is_causal=causal)
                     fo.backward(fdo)
                     for name, full, ref in zip(("out", "dq", "dk", "dv"), gathered, (fo.detach(), fq.grad, fk.grad, fv.grad)):
                         got = torch.stack([full[bb, hh] for (hh, bb) in sub]).unsqueeze(1)
@@ -633,7 +637,7 @@ def main():
                     if is_lazy:
                         o = fla.lazy_attention_triton(a, b_, c, bias_c, tau_c, window_size=512)
                     else:
-                        o = fla.adasplash(a, b_, c, alpha=alpha, niter=10, is_causal=causal, varlen=vl)
+                        o = fla.adasplash(a, b_, c, alpha=alpha, niter=args.niter, is_causal=causal, varlen=vl)
                     o.backward(ddo_[sl])
                     ev_comp[bi].record(s_comp)
                 with torch.cuda.stream(s_out):
@@ -735,7 +739,7 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong" if args.partition else "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": (f"{args.workload}: B={Bg} H={Hg} L={L} D={D} alpha={alpha} niter=10 causal={causal} "
+                "config": {"workload": (f"{args.workload}: B={Bg} H={Hg} L={L} D={D} alpha={alpha} niter={args.niter} causal={causal} "
                                         + ("in total, its (batch, head) pairs split over the GPUs" if args.partition else "per GPU")
                                         + ", fwd+bwd, seeded N(0,1) q,k,v,dO"),
                            "partition_check": partition_check,
